@@ -11,7 +11,8 @@ grouped by what layers need, and slots of fixed-size per-request state.
 * Pages are taken per step for exactly the tokens of that step (``extend``),
   counted as cached after the step ran (``commit``), and given back when the
   request ends (``release``) or - in a group with a window - once every token
-  on them is out of reach of all later queries.  A returned page is handed out
+  on them is out of reach of all later queries (pages that hold one of the
+  group's ``keep_first`` first tokens stay).  A returned page is handed out
   again first.  (The reference allocates a whole prompt at admission and
   frees only at the end: infernum-runtime/src/scheduler.rs:289-337.)
 * A request also holds one *slot* while it lives: the index of its row in
@@ -216,7 +217,7 @@ class CacheManager:
         for g in self.groups:
             need = self.pages_for(total_tokens)
             if g.spec.window > 0:
-                need = min(need, self.pages_for(g.spec.window + step_tokens) + 1)
+                need = min(need, self.pages_for(g.spec.window + step_tokens) + 1 + self.pages_for(g.spec.keep_first))
             out.append(need)
         return out
 
@@ -308,7 +309,7 @@ class CacheManager:
             # the next query sits at position >= num_tokens and reads keys
             # >= num_tokens - w + 1; page i holds [i*ps, (i+1)*ps)
             first_needed = rc.num_tokens - w + 1
-            i = 0
+            i = self.pages_for(g.spec.keep_first)  # the pages of the tokens that stay visible are kept
             while i < len(table) and (i + 1) * self.page_size <= first_needed:
                 if table[i] >= 0:
                     g.pool.free(table[i])

@@ -6,6 +6,13 @@
 //   expert's weight and 0 elsewhere.
 // One warp per row; the row is kept in shared memory and a chosen logit is
 // struck out there.
+//
+// A second way of scoring (ib_moe_route_scored): scores s = sigmoid(z); the experts
+// form `n_groups` equal groups of neighbours, a group's score is the sum of its
+// `group_top` largest scores, and only experts of the `keep` best groups can be
+// chosen (n_groups <= 1: all can); the `top` largest scores among those are
+// chosen, the lower index among equals, and are the weights as they are - or,
+// with `renorm`, divided by their sum.
 #include "common.cuh"
 
 using namespace ib;
@@ -108,6 +115,111 @@ IB_EXPORT int ib_moe_route(const float* logits, int ld, const float* bias, int E
     if ((size_t)E * sizeof(float) > 48 * 1024) return IB_ERR_TOO_LARGE;
     cudaError_t le = launch_kernel(moe_route_kernel, dim3(n_rows), dim3(32), (size_t)E * sizeof(float),
                                    (cudaStream_t)stream, logits, ld, bias, E, top, ids, weights, gate);
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+__global__ void moe_route_scored_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias,
+                                        int E, int top, int n_groups, int keep, int group_top, int renorm,
+                                        int* __restrict__ ids, float* __restrict__ weights,
+                                        float* __restrict__ gate) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float z[];  // [E] scores, struck out as they are chosen; then [n_groups] group scores
+    float* gs = z + E;
+    const int row = blockIdx.x, lane = threadIdx.x;
+    const float* src = logits + (size_t)row * ld;
+    for (int e = lane; e < E; e += 32) {
+        z[e] = 1.f / (1.f + expf(-(src[e] + (bias ? bias[e] : 0.f))));
+        if (gate) gate[(size_t)row * E + e] = 0.f;
+    }
+    __syncwarp();
+    if (n_groups > 1) {
+        const int per = E / n_groups;
+        // a lane a group: the sum of its group_top largest scores (lowest index among equals)
+        for (int g = lane; g < n_groups; g += 32) {
+            float sum = 0.f;
+            unsigned long long taken = 0ull;  // (groups of more than 64 experts: see the host check)
+            for (int k = 0; k < group_top && k < per; ++k) {
+                float best = -INFINITY;
+                int at = -1;
+                for (int i = 0; i < per; ++i) {
+                    if ((taken >> i) & 1ull) continue;
+                    const float v = z[g * per + i];
+                    if (v > best) { best = v; at = i; }
+                }
+                if (at < 0) break;
+                taken |= 1ull << at;
+                sum += best;
+            }
+            gs[g] = sum;
+        }
+        __syncwarp();
+        // lane 0 picks the best groups and strikes out the experts of the others
+        if (lane == 0) {
+            for (int k = 0; k < keep; ++k) {
+                float best = -INFINITY;
+                int at = -1;
+                for (int g = 0; g < n_groups; ++g)
+                    if (gs[g] > best) { best = gs[g]; at = g; }
+                if (at < 0) break;
+                gs[at] = -INFINITY;  // chosen: marked by -inf, told apart from the rest below
+            }
+        }
+        __syncwarp();
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / per] != -INFINITY) z[e] = -INFINITY;
+        __syncwarp();
+    }
+    float denom = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = E;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            if (v > best || (v == best && e < at)) { best = v; at = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at >= E) { at = k < E ? k : 0; best = 0.f; }  // nothing left to choose (a row of NaN): weight 0
+        denom += best;
+        if (lane == 0) {
+            ids[(size_t)row * top + k] = at;
+            weights[(size_t)row * top + k] = best;
+            z[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        for (int k = 0; k < top; ++k) {
+            float w = weights[(size_t)row * top + k];
+            if (renorm) {
+                w = w / denom;
+                weights[(size_t)row * top + k] = w;
+            }
+            if (gate) gate[(size_t)row * E + ids[(size_t)row * top + k]] = w;
+        }
+    }
+}
+
+IB_EXPORT int ib_moe_route_scored(const float* logits, int ld, const float* bias, int E, int top, int n_groups,
+                                  int keep, int group_top, int renorm, int* ids, float* weights, float* gate,
+                                  int n_rows, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!logits || !ids || !weights || E <= 0 || top <= 0 || top > E || ld < E) return IB_ERR_BAD_ARG;
+    if (n_groups > 1 && (E % n_groups || keep <= 0 || keep > n_groups || group_top <= 0 ||
+                         (long long)keep * (E / n_groups) < top))
+        return IB_ERR_BAD_ARG;
+    if (n_groups > 1 && E / n_groups > 64) return IB_ERR_TOO_LARGE;
+    const size_t smem = (size_t)(E + (n_groups > 1 ? n_groups : 0)) * sizeof(float);
+    if (smem > 48 * 1024) return IB_ERR_TOO_LARGE;
+    cudaError_t le = launch_kernel(moe_route_scored_kernel, dim3(n_rows), dim3(32), smem, (cudaStream_t)stream, logits,
+                                   ld, bias, E, top, n_groups, keep, group_top, renorm, ids, weights, gate);
     if (le != cudaSuccess) return (int)le;
     IB_LAUNCH_CHECK();
     return IB_OK;

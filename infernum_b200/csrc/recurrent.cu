@@ -15,6 +15,10 @@
 //   gated norm     v = y * silu(z); out = v / rms_group(v) * w   (rms over a group)
 //   qk norm        q, k <- x / rms(x) * w per head; the normed key and the key
 //                  as projected (the value) go to their pages
+//   delta prepare  what a gated delta rule's scan reads: convolved, activated and
+//                  unit-length queries and keys, values, write strengths and decays
+//   rope norm      bias, rotation, then a weightless RMS norm of queries, keys and
+//                  values per head; keys and values go to their pages
 // All arithmetic is 32-bit; small parameter vectors are float32.
 #include "common.cuh"
 
@@ -450,6 +454,235 @@ IB_EXPORT int ib_pointwise(void* a, const void* b, int b_stride, int act_dtype, 
     else if (act_dtype == 1)
         le = launch_kernel(pointwise_kernel<bf16>, dim3(grid), dim3(256), 0, s, (bf16*)a, (const bf16*)b, b_stride,
                            cols, total, op, ca, cb);
+    else
+        return IB_ERR_UNSUPPORTED;
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// delta_prepare: the pass before the scan of a gated delta rule.  A row of `x`
+// holds, from `c_off` on, C = 2 G dk + H dv channels q | k | v (G key heads of dk,
+// H value heads of dv) and, at `b_off` and `a_off`, H write-strength and H decay
+// pre-activations.  Per channel: the causal convolution (w [C, taps], the last
+// column the current token's, no bias; inputs before the entry's rows from the
+// last taps - 1 inputs kept in the state; taps 0: no convolution), then SiLU.
+// Per key head: q <- q / sqrt(sum q^2 + 1e-6) * dk^-1/2, k <- k / sqrt(sum k^2 + 1e-6).
+// Per value head: beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)).
+// Written in 32-bit the way the scan fetches: (k, q) pairs [G][rows][dk], values
+// [H][rows][dv], and (beta, g, k . q, 0) [H][rows].
+// One CTA per row; the row's channels meet in shared memory.
+template <typename T>
+__global__ void delta_prepare_kernel(const T* __restrict__ x, int x_stride, int c_off, int b_off, int a_off,
+                                     const float* __restrict__ w, int taps, const float* __restrict__ state,
+                                     long long state_stride, const int* __restrict__ row_entry,
+                                     const int* __restrict__ cu_rows, const int* __restrict__ slot_ids,
+                                     const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                     float2* __restrict__ kq, float* __restrict__ vo, float4* __restrict__ dd,
+                                     int n_rows, int G, int H, int dk, int dv) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float ch[];  // [C] channels, then [G] k . q
+    const int row = blockIdx.x;
+    const int C = 2 * G * dk + H * dv;
+    float* dots = ch + C;
+    int first = 0;
+    const float* st = nullptr;
+    if (taps > 1) {
+        const int e = row_entry[row];
+        first = cu_rows[e];
+        st = state + (long long)slot_ids[e] * state_stride;
+    }
+    const T* xr = x + c_off;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc;
+        if (taps >= 1) {
+            acc = 0.f;
+            for (int j = 0; j < taps; ++j) {
+                const int src = row - (taps - 1 - j);
+                float in;
+                if (src >= first) in = to_f32(xr[(size_t)src * x_stride + c]);
+                else in = st[(size_t)(taps - 1 - (first - src)) * C + c];
+                acc = fmaf(w[(size_t)c * taps + j], in, acc);
+            }
+        } else {
+            acc = to_f32(xr[(size_t)row * x_stride + c]);
+        }
+        ch[c] = silu_f(acc);
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int g = warp; g < G; g += nwarps) {
+        const float* q = ch + g * dk;
+        const float* k = ch + G * dk + g * dk;
+        float sq = 0.f, sk = 0.f, qk = 0.f;
+        for (int i = lane; i < dk; i += 32) {
+            sq = fmaf(q[i], q[i], sq);
+            sk = fmaf(k[i], k[i], sk);
+        }
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        const float iq = rsqrtf((float)dk) / sqrtf(sq + 1e-6f), ik = 1.f / sqrtf(sk + 1e-6f);
+        float2* dst = kq + ((size_t)g * n_rows + row) * dk;
+        for (int i = lane; i < dk; i += 32) {
+            const float kn = k[i] * ik, qn = q[i] * iq;
+            dst[i] = make_float2(kn, qn);
+            qk = fmaf(kn, qn, qk);
+        }
+        qk = warp_sum(qk);
+        if (lane == 0) dots[g] = qk;
+    }
+    const float* v = ch + 2 * G * dk;
+    for (int c = threadIdx.x; c < H * dv; c += blockDim.x)
+        vo[((size_t)(c / dv) * n_rows + row) * dv + c % dv] = v[c];
+    __syncthreads();
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float b = to_f32(x[(size_t)row * x_stride + b_off + h]);
+        const float a = to_f32(x[(size_t)row * x_stride + a_off + h]) + dt_bias[h];
+        const float sp = a > 20.f ? a : log1pf(expf(a));
+        dd[(size_t)h * n_rows + row] = make_float4(1.f / (1.f + expf(-b)), expf(-expf(a_log[h]) * sp),
+                                                   dots[h / (H / G)], 0.f);
+    }
+}
+
+IB_EXPORT int ib_delta_prepare(const void* x, int x_stride, int act_dtype, int c_off, int b_off, int a_off,
+                               const float* w, int taps, float* state, long long state_stride, const int* row_entry,
+                               const int* cu_rows, const int* slot_ids, const float* a_log, const float* dt_bias,
+                               void* kq, float* vo, void* dd, int n_rows, int n_entries, int G, int H, int dk, int dv,
+                               void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!x || !a_log || !dt_bias || !kq || !vo || !dd || G <= 0 || H <= 0 || H % G || dk <= 0 || dv <= 0 || taps < 0 ||
+        taps > IB_MAX_TAPS || ((uintptr_t)kq & 7) || ((uintptr_t)dd & 15))
+        return IB_ERR_BAD_ARG;
+    if (taps >= 1 && !w) return IB_ERR_BAD_ARG;
+    if (taps > 1 && (!state || !row_entry || !cu_rows || !slot_ids || n_entries <= 0)) return IB_ERR_BAD_ARG;
+    const int C = 2 * G * dk + H * dv;
+    const size_t smem = (size_t)(C + G) * sizeof(float);
+    if (smem > 200 * 1024) return IB_ERR_TOO_LARGE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = C >= 2048 ? 512 : 256;
+    const int gy = min(64, (C + 127) / 128);
+    cudaError_t le;
+    if (act_dtype == 0) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(delta_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        le = launch_kernel(delta_prepare_kernel<float>, dim3(n_rows), dim3(threads), smem, s, (const float*)x, x_stride,
+                           c_off, b_off, a_off, w, taps, (const float*)state, state_stride, row_entry, cu_rows,
+                           slot_ids, a_log, dt_bias, (float2*)kq, vo, (float4*)dd, n_rows, G, H, dk, dv);
+        if (le == cudaSuccess && taps > 1)
+            le = launch_kernel(conv_state_kernel<float>, dim3(n_entries, gy), dim3(128), 0, s, (const float*)x + c_off,
+                               x_stride, state, state_stride, cu_rows, slot_ids, C, taps);
+    } else if (act_dtype == 1) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(delta_prepare_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        le = launch_kernel(delta_prepare_kernel<bf16>, dim3(n_rows), dim3(threads), smem, s, (const bf16*)x, x_stride,
+                           c_off, b_off, a_off, w, taps, (const float*)state, state_stride, row_entry, cu_rows,
+                           slot_ids, a_log, dt_bias, (float2*)kq, vo, (float4*)dd, n_rows, G, H, dk, dv);
+        if (le == cudaSuccess && taps > 1)
+            le = launch_kernel(conv_state_kernel<bf16>, dim3(n_entries, gy), dim3(128), 0, s, (const bf16*)x + c_off,
+                               x_stride, state, state_stride, cu_rows, slot_ids, C, taps);
+    } else {
+        return IB_ERR_UNSUPPORTED;
+    }
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// rope_norm_append: rows of x hold nh query heads of hd, then nkv key heads of
+// hd, then nkv value heads of hdv.  One warp per (row, head):
+//   the head's bias is added (bias: one vector over the whole row, or null);
+//   queries and keys: the first rd dimensions are rotated, dimension i with
+//   i + rd/2, by the angle position * inv_freq[i] (32-bit product, sincosf);
+//   with `norm_qk` they are then divided by sqrt(mean(.^2) + eps) over hd;
+//   values: with `norm_v` divided by sqrt(mean(.^2) + eps) over hdv.
+// Queries are written back in place; keys and values go to their place in the
+// pages (key pool rows of hd, value pool rows of hdv).
+#define IB_RNA_MAX_DIM 1024
+template <typename T>
+__global__ void rope_norm_append_kernel(T* __restrict__ x, int x_stride, const float* __restrict__ bias,
+                                        const float* __restrict__ inv_freq, int rd, int norm_qk, int norm_v,
+                                        float eps, const int* __restrict__ positions,
+                                        const int* __restrict__ row_entry, const int* __restrict__ block_tables,
+                                        int max_blocks, T* __restrict__ k_pool, T* __restrict__ v_pool, int n_rows,
+                                        int nh, int nkv, int hd, int hdv, int page_size, int num_pages,
+                                        unsigned* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float hbuf[];  // [warps][max(hd, hdv)]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int per_row = nh + 2 * nkv;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    if (item >= (long long)n_rows * per_row) return;
+    const int row = (int)(item / per_row), head = (int)(item % per_row);
+    const bool is_v = head >= nh + nkv;
+    const int d = is_v ? hdv : hd;
+    const int col = is_v ? (nh + nkv) * hd + (head - nh - nkv) * hdv : head * hd;
+    float* buf = hbuf + (size_t)warp * max(hd, hdv);
+    T* p = x + (size_t)row * x_stride + col;
+    for (int i = lane; i < d; i += 32) buf[i] = to_f32(p[i]) + (bias ? bias[col + i] : 0.f);
+    __syncwarp();
+    const int pos = positions[row];
+    if (!is_v && rd > 0) {
+        const int rhalf = rd / 2;
+        for (int i = lane; i < rhalf; i += 32) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float a = buf[i], b = buf[i + rhalf];
+            buf[i] = a * cs - b * sn;
+            buf[i + rhalf] = b * cs + a * sn;
+        }
+        __syncwarp();
+    }
+    float inv = 1.f;
+    if (is_v ? norm_v : norm_qk) {
+        float ss = 0.f;
+        for (int i = lane; i < d; i += 32) ss = fmaf(buf[i], buf[i], ss);
+        ss = warp_sum(ss);
+        inv = 1.f / sqrtf(ss / (float)d + eps);
+    }
+    if (head < nh) {
+        for (int i = lane; i < d; i += 32) p[i] = from_f32<T>(buf[i] * inv);
+        return;
+    }
+    const int e = row_entry[row];
+    const int slot_idx = pos / page_size;
+    const int page = (pos >= 0 && slot_idx < max_blocks) ? block_tables[(size_t)e * max_blocks + slot_idx] : -1;
+    if (page < 0 || page >= num_pages) {
+        if (lane == 0) atomicOr(err, IB_FLAG_BAD_PAGE);
+        return;
+    }
+    const int g = is_v ? head - nh - nkv : head - nh;
+    T* dst = (is_v ? v_pool : k_pool) + (((size_t)page * nkv + g) * page_size + (pos % page_size)) * d;
+    for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(buf[i] * inv);
+}
+
+IB_EXPORT int ib_rope_norm_append(void* x, int x_stride, int act_dtype, const float* bias, const float* inv_freq,
+                                  int rd, int norm_qk, int norm_v, float eps, const int* positions,
+                                  const int* row_entry, const int* block_tables, int max_blocks, void* k_pool,
+                                  void* v_pool, int n_rows, int nh, int nkv, int hd, int hdv, int page_size,
+                                  int num_pages, unsigned* err, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!x || !positions || !row_entry || !block_tables || !k_pool || !v_pool || !err || nh <= 0 || nkv <= 0 ||
+        hd <= 0 || hdv <= 0 || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || rd < 0 || rd > hd || (rd & 1) ||
+        (rd > 0 && !inv_freq) || ((norm_qk || norm_v) && !(eps > 0.f)))
+        return IB_ERR_BAD_ARG;
+    if (hd > IB_RNA_MAX_DIM || hdv > IB_RNA_MAX_DIM) return IB_ERR_TOO_LARGE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long items = (long long)n_rows * (nh + 2 * nkv);
+    const unsigned grid = (unsigned)((items + 3) / 4);
+    const size_t smem = (size_t)4 * max(hd, hdv) * sizeof(float);
+    cudaError_t le;
+    if (act_dtype == 0)
+        le = launch_kernel(rope_norm_append_kernel<float>, dim3(grid), dim3(128), smem, s, (float*)x, x_stride, bias,
+                           inv_freq, rd, norm_qk, norm_v, eps, positions, row_entry, block_tables, max_blocks,
+                           (float*)k_pool, (float*)v_pool, n_rows, nh, nkv, hd, hdv, page_size, num_pages, err);
+    else if (act_dtype == 1)
+        le = launch_kernel(rope_norm_append_kernel<bf16>, dim3(grid), dim3(128), smem, s, (bf16*)x, x_stride, bias,
+                           inv_freq, rd, norm_qk, norm_v, eps, positions, row_entry, block_tables, max_blocks,
+                           (bf16*)k_pool, (bf16*)v_pool, n_rows, nh, nkv, hd, hdv, page_size, num_pages, err);
     else
         return IB_ERR_UNSUPPORTED;
     if (le != cudaSuccess) return (int)le;

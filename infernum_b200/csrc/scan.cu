@@ -7,6 +7,8 @@
 //   wkv:  o_t[j] = sum_i r_t[i] (S[i][j] + u[i] k_t[i] v_t[j])        (u only for the current token)
 //         S[i][j] <- w_t[i] S[i][j] + k_t[i] v_t[j]
 //   ssd:  S[n][p] <- a_t S[n][p] + B_t[n] (dt_t x_t[p]),   y_t[p] = sum_n C_t[n] S[n][p] + D x_t[p]
+//   delta: S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
+//         (a gated delta rule: the read-out sees the token's own write)
 //
 // Everything a token brings - (r, k, w, u k) per key channel and v for wkv; (B, C)
 // per state row, x, and (dt, a) per head for ssd - has been made in 32-bit by a
@@ -264,6 +266,108 @@ __global__ void __launch_bounds__(512) ssd_scan_kernel(const SsdParams p) {
     }
 }
 
+// The delta rule per column j of S, with the dot products taken on the state as
+// the token finds it so that the two of them run side by side instead of one
+// after the other:
+//   a = k . S_j,  b = q . S_j;   u = beta (v_j - g a);   o_j = g b + (k . q) u;   S_j <- g S_j + k u
+// which is S' = g S + k u^T and o = S'^T q written out (k . q comes prepared).
+struct DeltaParams {
+    const float* v;     // [heads][rows][P]
+    const float2* kq;   // [groups][rows][ROWS]: k, q (unit length; q scaled)
+    const float4* dd;   // [heads][rows]: beta, g, k . q, unused
+    int n_rows;
+    float* state;
+    long long state_stride;
+    const int* cu_rows;
+    const int* slot_ids;
+    float* out;         // [rows][heads * P]
+    int heads, groups, P, cols;
+};
+
+__global__ void __launch_bounds__(512) delta_scan_kernel(const DeltaParams p) {
+    pdl_wait();
+    extern __shared__ float4 smem4[];
+    float4* s_dd = smem4;                                             // [2][CHUNK_SSD]
+    float2* s_kq = reinterpret_cast<float2*>(s_dd + 2 * CHUNK_SSD);   // [2][CHUNK_SSD][ROWS]
+    float* s_v = reinterpret_cast<float*>(s_kq + 2 * CHUNK_SSD * ROWS);  // [2][CHUNK_SSD][cols]
+    const int e = blockIdx.x, head = blockIdx.y, j0 = blockIdx.z * p.cols;
+    const int first = p.cu_rows[e], end = p.cu_rows[e + 1];
+    if (end <= first) return;
+    const int part = threadIdx.x % SPLIT;
+    const int col_raw = threadIdx.x / SPLIT;
+    const bool active = col_raw < p.cols;
+    const int col = active ? col_raw : p.cols - 1;
+    float* st = p.state + (long long)p.slot_ids[e] * p.state_stride + (size_t)head * ROWS * p.P;
+    float* sc = st + (size_t)(j0 + col) * ROWS + part;
+    float S[RPT];
+#pragma unroll
+    for (int ii = 0; ii < RPT; ++ii) S[ii] = sc[ii * SPLIT];
+    const int inner = p.heads * p.P;
+    const int grp = head / (p.heads / p.groups);
+    const float2* kg = p.kq + (size_t)grp * p.n_rows * ROWS;
+    const float* vh = p.v + (size_t)head * p.n_rows * p.P + j0;
+    const float4* dh = p.dd + (size_t)head * p.n_rows;
+
+    auto fetch = [&](int c0, int buf) {
+        const int nt = min(CHUNK_SSD, end - c0);
+        float2* dk = s_kq + buf * CHUNK_SSD * ROWS;
+        float* dv = s_v + buf * CHUNK_SSD * p.cols;
+        const float2* src = kg + (size_t)c0 * ROWS;  // the chunk's (k, q) are one contiguous run
+        if (ROWS % 2 == 0) {
+            for (int idx = threadIdx.x; idx < nt * (ROWS / 2); idx += blockDim.x)
+                cp_async<16>(dk + 2 * idx, src + 2 * idx);
+        } else {
+            for (int idx = threadIdx.x; idx < nt * ROWS; idx += blockDim.x) cp_async<8>(dk + idx, src + idx);
+        }
+        for (int idx = threadIdx.x; idx < nt * p.cols; idx += blockDim.x)
+            cp_async<4>(dv + idx, vh + (size_t)(c0 + idx / p.cols) * p.P + idx % p.cols);
+        if (threadIdx.x < nt) cp_async<16>(s_dd + buf * CHUNK_SSD + threadIdx.x, dh + c0 + threadIdx.x);
+        cp_async_commit();
+    };
+    fetch(first, 0);
+    int buf = 0;
+    for (int c0 = first; c0 < end; c0 += CHUNK_SSD, buf ^= 1) {
+        const int nt = min(CHUNK_SSD, end - c0);
+        if (c0 + CHUNK_SSD < end) {
+            fetch(c0 + CHUNK_SSD, buf ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const float2* ck = s_kq + buf * CHUNK_SSD * ROWS + part;
+        const float* cv = s_v + buf * CHUNK_SSD * p.cols + col;
+        const float4* cd = s_dd + buf * CHUNK_SSD;
+#pragma unroll UNROLL
+        for (int t = 0; t < nt; ++t) {
+            const float vj = cv[t * p.cols];
+            const float4 d = cd[t];  // beta, g, k . q
+            const float2* f = ck + t * ROWS;
+            float2 kqr[RPT];
+            float a = 0.f, b = 0.f;
+#pragma unroll
+            for (int ii = 0; ii < RPT; ++ii) {
+                kqr[ii] = f[ii * SPLIT];
+                a = fmaf(kqr[ii].x, S[ii], a);
+                b = fmaf(kqr[ii].y, S[ii], b);
+            }
+            a = split_sum(a);
+            b = split_sum(b);
+            const float u = d.x * (vj - d.y * a);
+#pragma unroll
+            for (int ii = 0; ii < RPT; ++ii) S[ii] = fmaf(d.y, S[ii], kqr[ii].x * u);
+            if (active && part == 0)
+                p.out[(size_t)(c0 + t) * inner + (size_t)head * p.P + j0 + col] = fmaf(d.y, b, d.z * u);
+        }
+        __syncthreads();
+    }
+    pdl_trigger();
+    if (active) {
+#pragma unroll
+        for (int ii = 0; ii < RPT; ++ii) sc[ii * SPLIT] = S[ii];
+    }
+}
+
 IB_EXPORT int ib_scan_rows() { return ROWS; }
 IB_EXPORT int ib_scan_split() { return SPLIT; }
 
@@ -314,6 +418,30 @@ IB_EXPORT int ib_ssd_scan(const float* x, const void* bc, const void* dd, int n_
     if (smem > 48 * 1024) return IB_ERR_TOO_LARGE;
     cudaError_t le = launch_kernel_in_order(ssd_scan_kernel, dim3(n_entries, heads, col_slices), dim3(threads), smem,
                                    (cudaStream_t)stream, p);
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// v: float32 [heads][rows][P]; kq: float2 [groups][rows][ROWS]; dd: float4 [heads][rows];
+// out: float32 [rows][heads * P].
+IB_EXPORT int ib_delta_scan(const float* v, const void* kq, const void* dd, int n_rows, float* state,
+                            long long state_stride, const int* cu_rows, const int* slot_ids, float* out,
+                            int n_entries, int heads, int groups, int P, int col_slices, void* stream) {
+    if (n_entries <= 0) return IB_OK;
+    if (!v || !kq || !dd || !state || !cu_rows || !slot_ids || !out || heads <= 0 || groups <= 0 || heads % groups ||
+        ((uintptr_t)kq & 15) || ((uintptr_t)dd & 15))
+        return IB_ERR_BAD_ARG;
+    int cols, threads;
+    const int g = scan_geometry(P, col_slices, &cols, &threads);
+    if (g != IB_OK) return g;
+    DeltaParams p{v, (const float2*)kq, (const float4*)dd, n_rows, state, state_stride, cu_rows, slot_ids, out,
+                  heads, groups, P, cols};
+    const size_t smem = 2 * ((size_t)CHUNK_SSD * ROWS * sizeof(float2) + (size_t)CHUNK_SSD * sizeof(float4) +
+                             (size_t)CHUNK_SSD * cols * sizeof(float));
+    if (smem > 48 * 1024) return IB_ERR_TOO_LARGE;
+    cudaError_t le = launch_kernel_in_order(delta_scan_kernel, dim3(n_entries, heads, col_slices), dim3(threads), smem,
+                                            (cudaStream_t)stream, p);
     if (le != cudaSuccess) return (int)le;
     IB_LAUNCH_CHECK();
     return IB_OK;

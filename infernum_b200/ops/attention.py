@@ -16,21 +16,24 @@ from . import core
 
 def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     out: torch.Tensor, ctx, tables: torch.Tensor, n_heads: int, scale: float,
-                    window: int, rt, sink=None) -> None:
+                    window: int, rt, sink=None, keep_first: int = 0) -> None:
     """Attention of every row of the step over its request's pages.
 
     ``q`` holds the (already position-encoded) queries in its first
     ``n_heads * head_dim`` columns; keys and values of the step's own tokens
     are already in the pools.  ``sink`` (float32 [n_heads]): a logit per head
-    whose exponential is added to the softmax's denominator."""
+    whose exponential is added to the softmax's denominator.  ``keep_first``:
+    behind a window, the keys at positions below it stay visible.  Values may
+    have another size than keys (the value pool's last dimension)."""
     impl = rt.options.get("attention", "auto")
     if q.dtype == torch.bfloat16 and impl != "plain":
         from . import attention_fast
 
-        if attention_fast.run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=sink):
+        if attention_fast.run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=sink,
+                              keep_first=keep_first):
             return
     core.attention_plain(q, k_pool, v_pool, out, ctx.positions, ctx.row_entry, tables, n_heads,
-                         scale, window, rt.err, sink=sink)
+                         scale, window, rt.err, sink=sink, keep_first=keep_first)
 
 
 def latent_attention(q_abs: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, kv_rank: int, ctx,

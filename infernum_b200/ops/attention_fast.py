@@ -154,10 +154,12 @@ def _step_plan(ctx, G: int, nkv: int, tc_ok: bool, rt) -> dict:
     return plan
 
 
-def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=None) -> bool:
+def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=None, keep_first: int = 0) -> bool:
     num_pages, nkv, page_size, hd = k_pool.shape
     if not supported(hd):
         return False
+    if v_pool.shape[3] != hd or (keep_first > 0 and window > 0):
+        return False  # (values of another size, or kept first tokens behind a window: not in these kernels)
     if q.stride(0) % 2 or out.stride(0) % 2 or q.data_ptr() % 4 or out.data_ptr() % 4:
         return False  # (rows of an odd length, as a view of a wider product may have: the plain kernel takes them)
     if sink is not None and (sink.dtype != torch.float32 or sink.numel() != n_heads or not sink.is_contiguous()):

@@ -17,7 +17,7 @@ from ..csrc.build import load_module
 from ..errors import KernelError
 
 CORE_SOURCES = ["elementwise.cu", "attention_plain.cu", "gemm_plain.cu", "sampling.cu", "layernorm.cu",
-                "embed_hashed.cu", "latent.cu", "moe.cu", "hyper.cu", "recurrent.cu"]
+                "embed_hashed.cu", "latent.cu", "moe.cu", "hyper.cu", "recurrent.cu", "subnorm.cu"]
 
 _c_int = ctypes.c_int
 _c_float = ctypes.c_float
@@ -83,6 +83,25 @@ def core_lib() -> ctypes.CDLL:
                                        _c_void_p]
         lib.ib_attention_plain_ex.argtypes = lib.ib_attention_plain.argtypes[:19] + [_c_int, _c_int, _c_int, _c_int,
                                                                                   _c_void_p, _c_void_p, _c_void_p]
+        lib.ib_attention_plain_mask.argtypes = lib.ib_attention_plain.argtypes[:19] + [
+            _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p]
+        lib.ib_embed_dual.argtypes = [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                                      _c_void_p, _c_void_p]
+        lib.ib_sub_norm_add.argtypes = [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_float, _c_void_p, _c_int, _c_void_p,
+                                        _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p]
+        lib.ib_part_rmsnorm.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_int, _c_int,
+                                        _c_int, _c_void_p]
+        lib.ib_delta_prepare.argtypes = [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p,
+                                         _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                         _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p]
+        lib.ib_rope_norm_append.argtypes = [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+                                            _c_float, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p]
+        lib.ib_moe_route_scored.argtypes = [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                            _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p]
+        for fn in ("ib_attention_plain_mask", "ib_embed_dual", "ib_sub_norm_add", "ib_part_rmsnorm", "ib_delta_prepare",
+                   "ib_rope_norm_append", "ib_moe_route_scored"):
+            getattr(lib, fn).restype = _c_int
         lib.ib_gemm_plain_batched.argtypes = [_c_void_p, _c_int, _c_int, _c_ll, _c_void_p, _c_int, _c_int, _c_ll,
                                               _c_void_p, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int,
                                               _c_void_p]
@@ -425,35 +444,40 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: Optional[int] = No
 def attention_plain(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     out: torch.Tensor, positions: torch.Tensor, row_entry: torch.Tensor,
                     block_tables: torch.Tensor, n_heads: int, scale: float, window: int,
-                    err: torch.Tensor, sink: Optional[torch.Tensor] = None) -> None:
+                    err: torch.Tensor, sink: Optional[torch.Tensor] = None, keep_first: int = 0) -> None:
     """Causal attention of each row over its request's pages (32-bit arithmetic).
 
     ``q`` is [N, >= n_heads*hd] (a view into the qkv rows is fine), ``out`` is
-    [N, n_heads*hd]; pools are [pages, kv_heads, page_size, hd].  ``sink``
+    [N, n_heads*hdv]; the key pool is [pages, kv_heads, page_size, hd], the value
+    pool the same with rows of hdv values (hdv may differ from hd).  ``sink``
     (float32 [n_heads]): a logit per head that is added to the softmax's
-    denominator as exp(sink), with no key and no value behind it."""
+    denominator as exp(sink), with no key and no value behind it.
+    ``keep_first``: behind a window, the keys at positions below it stay visible."""
     require_cuda(q, k_pool, v_pool, out, positions, row_entry, block_tables, err, sink)
     _int32(positions, "positions")
     _int32(row_entry, "row_entry")
     _int32(block_tables, "block_tables")
     num_pages, nkv, page_size, hd = k_pool.shape
+    hdv = v_pool.shape[3]
     N = q.shape[0]
+    if v_pool.shape[:3] != k_pool.shape[:3] or not k_pool.is_contiguous() or not v_pool.is_contiguous():
+        raise KernelError("attention_plain: the pools must be contiguous and alike but for the value size")
     if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] < n_heads * hd \
-            or out.shape[1] < n_heads * hd:
+            or out.shape[1] < n_heads * hdv:
         raise KernelError("attention_plain: q/out rows are too short or not unit-stride")
     if not (q.dtype == k_pool.dtype == v_pool.dtype == out.dtype):
         raise KernelError("attention_plain: q, pools and out must share a dtype")
     if n_heads % nkv:
         raise KernelError(f"attention: {n_heads} heads are not a multiple of {nkv} kv heads")
-    if sink is not None:
-        if sink.dtype != torch.float32 or sink.shape != (n_heads,) or not sink.is_contiguous():
-            raise KernelError(f"attention_plain: sink must be contiguous float32 [{n_heads}]")
-        check(core_lib().ib_attention_plain_ex(q.data_ptr(), q.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
-                                               out.data_ptr(), out.stride(0), dtype_code(q.dtype),
-                                               positions.data_ptr(), row_entry.data_ptr(), block_tables.data_ptr(),
-                                               block_tables.shape[1], N, n_heads, nkv, hd, page_size, num_pages,
-                                               int(window), float(scale), hd, hd, hd, hd, sink.data_ptr(),
-                                               err.data_ptr(), stream_ptr(q)), "attention_plain")
+    if sink is not None and (sink.dtype != torch.float32 or sink.shape != (n_heads,) or not sink.is_contiguous()):
+        raise KernelError(f"attention_plain: sink must be contiguous float32 [{n_heads}]")
+    if sink is not None or keep_first > 0 or hdv != hd:
+        check(core_lib().ib_attention_plain_mask(q.data_ptr(), q.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
+                                                 out.data_ptr(), out.stride(0), dtype_code(q.dtype),
+                                                 positions.data_ptr(), row_entry.data_ptr(), block_tables.data_ptr(),
+                                                 block_tables.shape[1], N, n_heads, nkv, hd, page_size, num_pages,
+                                                 int(window), float(scale), hdv, hdv, hd, hdv, _ptr(sink),
+                                                 int(keep_first), err.data_ptr(), stream_ptr(q)), "attention_plain")
         return
     check(core_lib().ib_attention_plain(q.data_ptr(), q.stride(0), k_pool.data_ptr(),
                                         v_pool.data_ptr(), out.data_ptr(), out.stride(0),
@@ -959,3 +983,129 @@ def pointwise(a: torch.Tensor, b: Optional[torch.Tensor], op: str, ca: float = 1
     check(core_lib().ib_pointwise(a.data_ptr(), _ptr(b), b.stride(0) if b is not None else 0, dtype_code(a.dtype),
                                   a.shape[0], a.shape[1], _POINTWISE[op], float(ca), float(cb), stream_ptr(a)),
           "pointwise_" + op)
+
+
+# ---------------------------------------------------------------------------
+# Layers that norm a sub-layer's result in parts before adding it, a stream that
+# is a weighted sum of all layers' results, the pass before a delta rule's scan,
+# attention whose queries, keys and values are normed after the rotation, and
+# routing by sigmoid scores inside the best groups of experts.
+# ---------------------------------------------------------------------------
+def embed_dual(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, act: Optional[torch.Tensor],
+               err: torch.Tensor) -> None:
+    """out[t, :] = table[ids[t], :] into a float32 stream and, when given, into
+    ``act`` in the activation dtype."""
+    require_cuda(ids, table, out, act, err)
+    _int32(ids, "ids")
+    n = ids.numel()
+    V, H = table.shape
+    if out.dtype != torch.float32 or out.shape != (n, H) or not out.is_contiguous() or not table.is_contiguous():
+        raise KernelError(f"embed_dual: out must be contiguous float32 [{n}, {H}], the table contiguous")
+    if act is not None and (act.shape != (n, H) or not act.is_contiguous()):
+        raise KernelError(f"embed_dual: act must be contiguous [{n}, {H}]")
+    check(core_lib().ib_embed_dual(ids.data_ptr(), table.data_ptr(), dtype_code(table.dtype), out.data_ptr(),
+                                   _ptr(act), dtype_code(act.dtype) if act is not None else 0, n, H, V,
+                                   err.data_ptr(), stream_ptr(out)), "embed_dual")
+
+
+def sub_norm_add(x_in: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, parts: int, eps: float,
+                 out_res: torch.Tensor, out_act: Optional[torch.Tensor], results: Optional[torch.Tensor] = None,
+                 slot: int = 0, coef: Optional[torch.Tensor] = None) -> None:
+    """``X = x_in + n(y)`` with ``n`` the RMS norm over ``parts`` equal consecutive
+    parts of a row times ``weight`` (float32).  Without ``results``: ``out_res = X``.
+    With ``results`` (float32 [slots, N, W]): ``results[slot] = X`` and ``out_res =
+    sum_{j <= slot} coef[j] results[j]``.  ``out_act`` gets ``out_res`` rounded to the
+    activation dtype.  ``x_in`` and ``out_res`` may be one buffer."""
+    require_cuda(x_in, y, weight, out_res, out_act, results, coef)
+    N, W = x_in.shape
+    for t, name in ((x_in, "x_in"), (out_res, "out_res")):
+        if t.dtype != torch.float32 or t.shape != (N, W) or not t.is_contiguous():
+            raise KernelError(f"sub_norm_add: {name} must be contiguous float32 [{N}, {W}]")
+    if y.shape != (N, W) or not y.is_contiguous() or (out_act is not None and (
+            out_act.shape != (N, W) or out_act.dtype != y.dtype or not out_act.is_contiguous())):
+        raise KernelError("sub_norm_add: y and out_act must be contiguous [N, W] of one dtype")
+    _f32_vec(weight, W, "sub_norm_add: weight")
+    if parts <= 0 or W % parts:
+        raise KernelError(f"sub_norm_add: a row of {W} does not split in {parts} parts")
+    if results is not None:
+        if results.dtype != torch.float32 or results.dim() != 3 or results.shape[1:] != (N, W) \
+                or not results.is_contiguous() or not 1 <= slot < results.shape[0]:
+            raise KernelError("sub_norm_add: results must be contiguous float32 [slots, N, W] with the slot inside")
+        _f32_vec(coef, slot + 1, "sub_norm_add: coef")
+    check(core_lib().ib_sub_norm_add(x_in.data_ptr(), y.data_ptr(), dtype_code(y.dtype), weight.data_ptr(), float(eps),
+                                     _ptr(results), int(slot), _ptr(coef), out_res.data_ptr(), _ptr(out_act), N, W,
+                                     int(parts), stream_ptr(y)), "sub_norm_add")
+
+
+def part_rmsnorm(x: torch.Tensor, weight: torch.Tensor, parts: int, eps: float, out: torch.Tensor,
+                 row_idx: Optional[torch.Tensor] = None) -> None:
+    """out = n(x) for all rows of the float32 ``x`` or for those ``row_idx`` names."""
+    require_cuda(x, weight, out, row_idx)
+    _int32(row_idx, "row_idx")
+    N, W = x.shape
+    n_out = N if row_idx is None else row_idx.numel()
+    if x.dtype != torch.float32 or not x.is_contiguous() or out.shape != (n_out, W) or not out.is_contiguous():
+        raise KernelError(f"part_rmsnorm: x contiguous float32 [N, {W}], out contiguous [{n_out}, {W}]")
+    _f32_vec(weight, W, "part_rmsnorm: weight")
+    if parts <= 0 or W % parts:
+        raise KernelError(f"part_rmsnorm: a row of {W} does not split in {parts} parts")
+    check(core_lib().ib_part_rmsnorm(x.data_ptr(), _ptr(row_idx), weight.data_ptr(), float(eps), out.data_ptr(),
+                                     dtype_code(out.dtype), n_out, W, int(parts), stream_ptr(x)), "part_rmsnorm")
+
+
+def rope_norm_append(x: torch.Tensor, bias: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], rotary_dim: int,
+                     norm_qk: bool, norm_v: bool, eps: float, n_heads: int, n_kv_heads: int, head_dim: int,
+                     positions: torch.Tensor, row_entry: torch.Tensor, block_tables: torch.Tensor,
+                     k_pool: torch.Tensor, v_pool: torch.Tensor, err: torch.Tensor) -> None:
+    """Rows of ``x`` hold ``n_heads`` query heads and ``n_kv_heads`` key heads of
+    ``head_dim`` and then ``n_kv_heads`` value heads of the value pool's width.  The
+    bias (float32, one value per column of those) is added; queries and keys are
+    rotated in their first ``rotary_dim`` dimensions and then, with ``norm_qk``,
+    divided by their root mean square per head; values, with ``norm_v``, likewise.
+    Queries are written back in place, keys and values to their pages."""
+    require_cuda(x, bias, inv_freq, positions, row_entry, block_tables, k_pool, v_pool, err)
+    _int32(positions, "positions")
+    _int32(row_entry, "row_entry")
+    _int32(block_tables, "block_tables")
+    num_pages, nkv_pool, page_size, hd_pool = k_pool.shape
+    hdv = v_pool.shape[3]
+    cols = (n_heads + n_kv_heads) * head_dim + n_kv_heads * hdv
+    if x.dim() != 2 or x.stride(1) != 1 or x.shape[1] < cols:
+        raise KernelError("rope_norm_append: x rows must hold the query, key and value heads with unit inner stride")
+    if nkv_pool != n_kv_heads or hd_pool != head_dim or v_pool.shape[:3] != k_pool.shape[:3] or k_pool.dtype != x.dtype \
+            or v_pool.dtype != x.dtype or not k_pool.is_contiguous() or not v_pool.is_contiguous():
+        raise KernelError("rope_norm_append: pools must be contiguous [pages, kv_heads, page_size, size] of x's dtype")
+    _f32_vec(bias, cols, "rope_norm_append: bias")
+    if rotary_dim > 0:
+        _f32_vec(inv_freq, rotary_dim // 2, "rope_norm_append: inv_freq")
+        if inv_freq is None:
+            raise KernelError("rope_norm_append: a rotation needs its frequencies")
+    check(core_lib().ib_rope_norm_append(x.data_ptr(), x.stride(0), dtype_code(x.dtype), _ptr(bias), _ptr(inv_freq),
+                                         int(rotary_dim), 1 if norm_qk else 0, 1 if norm_v else 0, float(eps),
+                                         positions.data_ptr(), row_entry.data_ptr(), block_tables.data_ptr(),
+                                         block_tables.shape[1], k_pool.data_ptr(), v_pool.data_ptr(), x.shape[0],
+                                         n_heads, n_kv_heads, head_dim, hdv, page_size, num_pages, err.data_ptr(),
+                                         stream_ptr(x)), "rope_norm_append")
+
+
+def moe_route_scored(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids: torch.Tensor,
+                     weights: torch.Tensor, gate: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 1,
+                     group_top: int = 2, renorm: bool = False) -> None:
+    """Routing by ``s = sigmoid(logits + bias)``: the experts form ``groups`` equal
+    groups of neighbours, a group's score is the sum of its ``group_top`` largest
+    scores, only experts of the ``keep`` best groups can be chosen; the ``top``
+    largest scores among them are chosen and are the weights (``renorm``: divided
+    by their sum).  Outputs as ``moe_route``."""
+    require_cuda(logits, bias, ids, weights, gate)
+    _int32(ids, "ids")
+    N, E = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or ids.shape != (N, top) \
+            or weights.shape != (N, top) or weights.dtype != torch.float32 or not weights.is_contiguous():
+        raise KernelError("moe_route_scored: logits float32 [N, E], ids int32 [N, top], weights float32 [N, top]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.shape != (E,) or not bias.is_contiguous()):
+        raise KernelError("moe_route_scored: the bias must be float32 [E]")
+    if gate is not None and (gate.dtype != torch.float32 or gate.shape != (N, E) or not gate.is_contiguous()):
+        raise KernelError("moe_route_scored: gate must be contiguous float32 [N, E]")
+    check(core_lib().ib_moe_route_scored(logits.data_ptr(), logits.stride(0), _ptr(bias), E, int(top), int(groups),
+                                         int(keep), int(group_top), 1 if renorm else 0, ids.data_ptr(),
+                                         weights.data_ptr(), _ptr(gate), N, stream_ptr(logits)), "moe_route_scored")

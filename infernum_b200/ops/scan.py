@@ -1,7 +1,7 @@
 """The scans of recurrent mixers (``scan.cu``): one compiled module per number
 of rows of the per-head state matrix, built when a model first needs it.
 
-``wkv_scan`` and ``ssd_scan`` walk every entry's rows in order from the state in
+``wkv_scan``, ``ssd_scan`` and ``delta_scan`` walk every entry's rows in order from the state in
 the request's slot and leave the new state there; what they need to know about
 the step (entries, slots) they read from the step's device tensors, so a
 recorded step replays them for other requests.
@@ -10,7 +10,7 @@ recorded step replays them for other requests.
 from __future__ import annotations
 
 import ctypes
-from typing import Dict
+from typing import Dict, Optional
 
 import torch
 
@@ -34,7 +34,9 @@ def lib_for(rows: int) -> ctypes.CDLL:
                                     _c_int, _c_int, _c_int, _c_int, _c_void_p]
         lib.ib_ssd_scan.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_ll, _c_void_p,
                                     _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p]
-        for fn in ("ib_wkv_scan", "ib_ssd_scan", "ib_scan_rows", "ib_scan_split"):
+        lib.ib_delta_scan.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p,
+                                      _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p]
+        for fn in ("ib_wkv_scan", "ib_ssd_scan", "ib_delta_scan", "ib_scan_rows", "ib_scan_split"):
             getattr(lib, fn).restype = _c_int
         if lib.ib_scan_rows() != rows:
             raise KernelError(f"scan module for {rows} state rows was built for another size")
@@ -154,3 +156,53 @@ def ssd_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: 
     core.check(lib.ib_ssd_scan(x32.data_ptr(), bc.data_ptr(), dd.data_ptr(), N, d_skip.data_ptr(), ptr, stride,
                                ctx.cu_rows.data_ptr(), ctx.slot_ids.data_ptr(), out.data_ptr(), ctx.n_entries, heads,
                                groups, vdim, slices, core.stream_ptr(xbc)), "ssd_scan")
+
+
+def delta_scan(proj: torch.Tensor, c_off: int, b_off: int, a_off: int, conv_w: Optional[torch.Tensor],
+               a_log: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, state_offset: int, conv_offset: int,
+               ctx, out: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, rt) -> None:
+    """A gated delta rule.  Per value head, with S [dim, vdim] from ``state[slot, offset:]``
+    (stored column by column) and the head's key head ``h // (heads / kv_heads)``:
+    ``S <- g S``, ``u = beta (v - S^T k)``, ``S <- S + k u^T``, ``o = S^T q``.
+    A row of ``proj`` holds, from column ``c_off``, the channels ``q | k`` (kv_heads x dim
+    each) and ``v`` (heads x vdim), and at ``b_off`` / ``a_off`` the ``heads`` pre-activations
+    of ``beta = sigmoid(.)`` and of ``g = exp(-exp(a_log) softplus(. + dt_bias))``.  The
+    channels first pass a causal convolution (``conv_w`` float32 [channels, taps], last
+    column the current token's; None: none) and SiLU; q and k are then scaled to unit
+    length, q also by ``dim ** -0.5``.  The convolution's last ``taps - 1`` inputs are
+    carried at ``conv_offset`` of the state.  ``out`` float32 [N, heads * vdim].
+    Two kernels as for the other scans: the parallel pass and the scan."""
+    core.require_cuda(proj, conv_w, a_log, dt_bias, state, out)
+    N = proj.shape[0]
+    C = 2 * kv_heads * dim + heads * vdim
+    if proj.dim() != 2 or proj.stride(1) != 1 or heads % kv_heads or min(c_off, b_off, a_off) < 0 \
+            or max(c_off + C, b_off + heads, a_off + heads) > proj.shape[1]:
+        raise KernelError("delta_scan: the projected rows do not hold q | k | v and the two gate pre-activations")
+    if out.shape != (N, heads * vdim) or out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("delta_scan: out must be contiguous float32 [N, heads * vdim]")
+    for t, name in ((a_log, "a_log"), (dt_bias, "dt_bias")):
+        if t.dtype != torch.float32 or t.numel() != heads or not t.is_contiguous():
+            raise KernelError(f"delta_scan: {name} must be contiguous float32 [{heads}]")
+    taps = 0
+    if conv_w is not None:
+        taps = conv_w.shape[1]
+        if conv_w.dtype != torch.float32 or conv_w.shape[0] != C or not conv_w.is_contiguous():
+            raise KernelError(f"delta_scan: the convolution's weight must be contiguous float32 [{C}, taps]")
+    lib = lib_for(dim)
+    dev = proj.device
+    kq = torch.empty((kv_heads, N, dim, 2), dtype=torch.float32, device=dev)
+    v32 = torch.empty((heads, N, vdim), dtype=torch.float32, device=dev)
+    dd = torch.empty((heads, N, 4), dtype=torch.float32, device=dev)
+    conv_ptr, conv_stride = _state_ptr(state, conv_offset)
+    core.check(core.core_lib().ib_delta_prepare(
+        proj.data_ptr(), proj.stride(0), core.dtype_code(proj.dtype), int(c_off), int(b_off), int(a_off),
+        conv_w.data_ptr() if conv_w is not None else None, taps, conv_ptr, conv_stride, ctx.row_entry.data_ptr(),
+        ctx.cu_rows.data_ptr(), ctx.slot_ids.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(), kq.data_ptr(),
+        v32.data_ptr(), dd.data_ptr(), N, ctx.n_entries, kv_heads, heads, dim, vdim, core.stream_ptr(proj)),
+        "delta_prepare")
+    ptr, stride = _state_ptr(state, state_offset)
+    sm = rt.options.get("sm_count") or SM_COUNT_FALLBACK
+    slices = choose_col_slices(ctx.n_entries, heads, vdim, lib.ib_scan_split(), sm)
+    core.check(lib.ib_delta_scan(v32.data_ptr(), kq.data_ptr(), dd.data_ptr(), N, ptr, stride, ctx.cu_rows.data_ptr(),
+                                 ctx.slot_ids.data_ptr(), out.data_ptr(), ctx.n_entries, heads, kv_heads, vdim, slices,
+                                 core.stream_ptr(proj)), "delta_scan")

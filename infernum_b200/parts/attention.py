@@ -28,7 +28,14 @@ key as projected, before any norm);
 ``sink`` (a tensor name: one learned logit per head whose exponential is added
 to the softmax's denominator; it has no key and no value and is not scaled);
 ``gate`` (a tensor name: the concatenated heads are multiplied by
-``sigmoid(W_gate x)`` before the output projection).
+``sigmoid(W_gate x)`` before the output projection);
+``v_head_dim`` (the size of a value head when it differs from a key's);
+``biases`` ({"q": name, "k": name, "v": name}: biases of the three projections);
+``unit_norm`` ({"eps": e, "value": bool}: after the rotation, queries and keys are
+divided by their root mean square per head, without a weight; with ``value`` each
+value head likewise, and it is cached so); may be combined with a rotary ``position``;
+``keep_first`` (with a window: the first so many tokens of a request stay visible
+to every later query, at their own positions).
 """
 
 from __future__ import annotations
@@ -74,11 +81,24 @@ class Attention(Mixer):
             self.qk_norm = {"q": self.prefix + qk_norm["q"], "k": self.prefix + qk_norm["k"],
                             "eps": float(qk_norm["eps"])}
         self.value_from_key = bool(params.get("value_from_key", False))
+        self.v_head_dim = int(params.get("v_head_dim") or self.head_dim)
+        self.keep_first = int(params.get("keep_first") or 0) if self.window > 0 else 0
+        biases = params.get("biases")
+        self.bias_names = {k: self.prefix + biases[k] for k in ("q", "k", "v")} if biases else None
+        unit = params.get("unit_norm")
+        self.unit_norm = {"eps": float(unit["eps"]), "value": bool(unit.get("value", False))} if unit else None
+        self.fused_prep = bool(self.bias_names or self.unit_norm or self.v_head_dim != self.head_dim)
+        self.bias = None
         self.sink_name = self.prefix + params["sink"] if params.get("sink") else None
         self.gate_name = self.prefix + params["gate"] if params.get("gate") else None
         if (self.qk_norm or self.value_from_key) and self.position is not None:
             raise ConfigError("attention: normed queries and keys, or values taken from keys, "
                               "are not combined with a position encoding")
+        if self.fused_prep and (self.qk_norm or self.value_from_key or self.kv_shared or self.gate_name):
+            raise ConfigError("attention: biases, weightless norms after the rotation or values of another size "
+                              "are not combined with weighted norms, values taken from keys, a gate or a shared cache")
+        if self.fused_prep and self.position is not None and not isinstance(self.position, RotaryEmbedding):
+            raise ConfigError("attention: biases and weightless norms go with a rotary position encoding or none")
         if (self.qk_norm or self.value_from_key) and self.kv_shared:
             raise ConfigError("attention: normed keys or values taken from keys need a cache of the layer's own")
         self.qkv: Optional[Linear] = None
@@ -87,18 +107,25 @@ class Attention(Mixer):
 
     # ---- declarations -----------------------------------------------------
     def cache_spec(self) -> Optional[PagedCacheSpec]:
+        if self.v_head_dim != self.head_dim or self.keep_first:
+            return PagedCacheSpec(self.num_kv_heads, self.head_dim, self.window, v_head_dim=self.v_head_dim,
+                                  keep_first=self.keep_first)
         return PagedCacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         qd, kvd = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        vd, od = self.num_kv_heads * self.v_head_dim, self.num_heads * self.v_head_dim
         specs = {
             self.names["q"]: WeightSpec((qd, self.hidden_size)),
-            self.names["o"]: WeightSpec((self.hidden_size, qd)),
+            self.names["o"]: WeightSpec((self.hidden_size, od)),
         }
         if not self.kv_shared:
             specs[self.names["k"]] = WeightSpec((kvd, self.hidden_size))
             if not self.value_from_key:
-                specs[self.names["v"]] = WeightSpec((kvd, self.hidden_size))
+                specs[self.names["v"]] = WeightSpec((vd, self.hidden_size))
+        if self.bias_names:
+            for k, n in ((("q"), qd), ("k", kvd), ("v", vd)):
+                specs[self.bias_names[k]] = WeightSpec((n,), init="normal", std=0.1)
         if self.qk_norm:
             specs[self.qk_norm["q"]] = WeightSpec((self.head_dim,), init="norm")
             specs[self.qk_norm["k"]] = WeightSpec((self.head_dim,), init="norm")
@@ -122,6 +149,9 @@ class Attention(Mixer):
             self.k_norm_w = weights[self.qk_norm["k"]].to(torch.float32).contiguous()
         if self.sink_name:
             self.sink = weights[self.sink_name].to(torch.float32).contiguous()
+        if self.bias_names:
+            self.bias = torch.cat([weights[self.bias_names[k]].to(torch.float32).view(-1)
+                                   for k in ("q", "k", "v")]).contiguous()
 
     def weight_bytes(self) -> int:
         return self.qkv.nbytes + self.o.nbytes
@@ -141,6 +171,16 @@ class Attention(Mixer):
         nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         qkv = projected if projected is not None else self.qkv(x)  # [N, (nh + 2 nkv) hd (+ gate)], or [N, nh hd] when the cache is shared
         tables = ctx.block_tables[cache.group]
+        if self.fused_prep:
+            if not cache.owner:
+                raise ConfigError("attention with biases or weightless norms must own its cache")
+            rotary = self.position
+            core.rope_norm_append(qkv, self.bias, rotary.inv_freq if rotary else None,
+                                  rotary.rotary_dim if rotary else 0, self.unit_norm is not None,
+                                  bool(self.unit_norm and self.unit_norm["value"]),
+                                  self.unit_norm["eps"] if self.unit_norm else 1e-6, nh, nkv, hd, ctx.positions,
+                                  ctx.row_entry, tables, cache.k_pool, cache.v_pool, self.rt.err)
+            return self._attend(qkv, ctx, cache, tables)
         if self.qk_norm or self.value_from_key:
             if not cache.owner:
                 raise ConfigError("attention with normed keys must own its cache")
@@ -168,9 +208,9 @@ class Attention(Mixer):
 
     def _attend(self, qkv: torch.Tensor, ctx, cache, tables) -> torch.Tensor:
         nh, hd = self.num_heads, self.head_dim
-        out = torch.empty((qkv.shape[0], nh * hd), dtype=qkv.dtype, device=qkv.device)
+        out = torch.empty((qkv.shape[0], nh * self.v_head_dim), dtype=qkv.dtype, device=qkv.device)
         attn_ops.paged_attention(qkv, cache.k_pool, cache.v_pool, out, ctx, tables, nh,
-                                 self.scale, self.window, self.rt, sink=self.sink)
+                                 self.scale, self.window, self.rt, sink=self.sink, keep_first=self.keep_first)
         if self.gate_name:
             g0 = self.qkv.out_features - nh * hd
             core.pointwise(out, qkv[:, g0: g0 + nh * hd], "sigmoid_gate")

@@ -115,12 +115,15 @@ class PagedCacheSpec:
     ``window`` tokens are ever read, so older pages can be given back.
     ``v_head_dim``: the size of a value when it differs from a key's; 0 means
     the mixer keeps no values of their own (a latent cache, where keys and
-    values are made from the one cached vector): only the key pool exists."""
+    values are made from the one cached vector): only the key pool exists.
+    ``keep_first`` (with a window): the first so many tokens of a request stay
+    visible however far back they lie, so the pages that hold them are kept."""
 
     kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: Optional[int] = None
+    keep_first: int = 0
 
     @property
     def value_dim(self) -> int:
@@ -308,6 +311,10 @@ class ResidualStream:
         # sub-layers read the stream itself (norm after the sum); valid while
         # nothing is pending.  In a float32 engine it is the residual.
         self.act = act
+        # For models whose stream between layers is a weighted sum of all layers'
+        # results: float32 [slots, N, hidden], slot 0 the embedding's output, slot
+        # j the result of layer j - 1; filled as the layers run.
+        self.results: Optional[torch.Tensor] = None
 
     def push(self, delta: torch.Tensor, write=None) -> None:
         if self.pending is not None:

@@ -15,6 +15,11 @@ and writes ``x_t <- sum_s mix_q[s, t] x_s + out_q[t] y`` into all streams at
 once (``mix`` is indexed [from, to]).  The write is not done here either: it is
 pushed on the stream with its coefficients, and the next read-and-norm kernel
 does write, read and norm in one pass over the row.
+
+``subnorm``: the norm sits on the sub-layer's result: ``x <- x + norm1(mixer(x))``,
+then ``x <- x + norm2(ffn(x))``; the sub-layers read the stream itself.  With
+``depth_average`` the layer's result is kept and what goes on is a weighted sum
+of the embedding's output and all layers' results so far.
 """
 
 from __future__ import annotations
@@ -125,3 +130,59 @@ class PostNormBlock(Block):
             norm2.renorm(stream, self.alpha)
         elif norm2 is not None and getattr(norm2, "present", True):
             norm2.renorm(stream, self.alpha)
+
+
+@BLOCKS.register("subnorm")
+class SubNormBlock(Block):
+    """``x <- x + norm1(mixer(x))`` and then ``x <- x + norm2(ffn(x))``: the sub-layers
+    read the stream itself (``stream.act``, its rounding to the activation dtype),
+    and their results are normed before they are added, in 32-bit.  The norms must
+    offer ``add_normed`` (``part_rmsnorm`` does).
+
+    Parameters: ``depth_average`` (a tensor name or None) and ``depth_index`` i:
+    with X_0 the embedding's output and X_(j+1) the result of layer j, the stream
+    after this layer is ``sum_{j <= i + 1} w[j] X_j``, ``w`` the named tensor of
+    i + 2 values.  The sum is taken by the kernel of the layer's last norm.  The
+    embedding must then keep room for the results (``result_slots``).
+    Parts: ``norm1``, ``mixer``, and optionally ``ffn`` with ``norm2``.
+    """
+
+    def __init__(self, params, rt, parts):
+        super().__init__(params, rt, parts)
+        missing = [r for r in ("norm1", "mixer") if r not in parts]
+        if "ffn" in parts and "norm2" not in parts:
+            missing.append("norm2")
+        if missing:
+            raise ConfigError(f"subnorm block {params.get('name', '')!r} lacks parts {missing}")
+        for role in ("norm1", "norm2"):
+            if role in parts and not hasattr(parts[role], "add_normed"):
+                raise ConfigError(f"subnorm block: the {parts[role].kind!r} norm cannot norm a sub-layer's result")
+        self.depth_name = params.get("depth_average")
+        self.depth_index = int(params.get("depth_index", 0))
+        self.depth_coef = None
+
+    def weight_specs(self):
+        specs = super().weight_specs()
+        if self.depth_name:
+            specs[self.depth_name] = WeightSpec((self.depth_index + 2,), init="normal", std=0.3)
+        return specs
+
+    def bind(self, weights) -> None:
+        super().bind(weights)
+        if self.depth_name:
+            self.depth_coef = weights[self.depth_name].to(torch.float32).contiguous()
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        p = self.parts
+        if stream.act is None:
+            raise ConfigError("subnorm block: the stream carries no activation copy (wrong embedding?)")
+        depth = None
+        if self.depth_coef is not None:
+            if stream.results is None or stream.results.shape[0] < self.depth_index + 2:
+                raise ConfigError("subnorm block: the stream keeps no room for the layers' results")
+            depth = (self.depth_index + 1, self.depth_coef)
+        ffn = p.get("ffn")
+        y = p["mixer"].forward(stream.act, ctx, cache)
+        p["norm1"].add_normed(stream, y, depth if ffn is None else None)
+        if ffn is not None:
+            p["norm2"].add_normed(stream, ffn.forward(stream.act, ctx), depth)

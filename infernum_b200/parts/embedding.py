@@ -24,12 +24,38 @@ from .linear import Linear
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
+    """Parameters: ``vocab_size``, ``hidden_size``, ``weight``; ``act`` (True: the
+    stream also carries its rounding to the activation dtype, for layers whose
+    sub-layers read the stream itself); ``result_slots`` (n > 0: the stream keeps
+    room for n results - the embedding's output, in slot 0, and every layer's -
+    for layers that hand on a weighted sum of them)."""
+
     def __init__(self, params, rt: Runtime):
         super().__init__(params, rt)
         self.vocab_size = int(params["vocab_size"])
         self.hidden_size = int(params["hidden_size"])
         self.weight_name = params["weight"]
+        self.with_act = bool(params.get("act", False))
+        self.result_slots = int(params.get("result_slots") or 0)
         self.weight: Optional[torch.Tensor] = None
+
+    def forward_step(self, ctx, cache) -> ResidualStream:
+        if not self.with_act and not self.result_slots:
+            return ResidualStream(self.forward(ctx.token_ids))
+        n, dev = ctx.token_ids.numel(), ctx.token_ids.device
+        results = None
+        if self.result_slots:
+            results = torch.empty((self.result_slots, n, self.hidden_size), dtype=torch.float32, device=dev)
+            out = results[0]
+        else:
+            out = torch.empty((n, self.hidden_size), dtype=torch.float32, device=dev)
+        act = None
+        if self.with_act and not self.rt.is_fp32:
+            act = torch.empty((n, self.hidden_size), dtype=self.rt.dtype, device=dev)
+        core.embed_dual(ctx.token_ids, self.weight, out, act, self.rt.err)
+        stream = ResidualStream(out, (out if act is None else act) if self.with_act else None)
+        stream.results = results
+        return stream
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         return {self.weight_name: WeightSpec((self.vocab_size, self.hidden_size))}

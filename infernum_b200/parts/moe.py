@@ -19,7 +19,12 @@ Parameters: ``hidden_size``, ``expert_size`` (ff), ``experts``, ``top``,
 ``activation`` ("silu" | "gelu_tanh"), ``prefix``, ``expert_names`` (format of
 an expert's tensors behind the prefix, default "e{e}.{w}" with w in gate, up,
 down), ``router`` and ``router_bias`` (names behind the prefix; bias None for
-none).
+none); ``scoring``: "softmax_top" (default, as above) or "sigmoid": the scores
+are ``sigmoid(z)``, the ``top`` largest are chosen and are the weights as they
+are (``renormalize``: divided by their sum); with ``groups`` ({"count", "keep",
+"top": 2}) the experts form ``count`` equal groups of neighbours, a group's
+score is the sum of its ``top`` largest scores and only experts of the best
+``keep`` groups can be chosen.
 """
 
 from __future__ import annotations
@@ -52,6 +57,23 @@ class MixtureOfExperts(FeedForward):
         self.router_name = self.prefix + params.get("router", "router")
         bias = params.get("router_bias", "router.b")
         self.bias_name = self.prefix + bias if bias else None
+        self.scoring = params.get("scoring", "softmax_top")
+        if self.scoring not in ("softmax_top", "sigmoid"):
+            raise ConfigError(f"mixture of experts: unknown scoring {self.scoring!r} (softmax_top, sigmoid)")
+        self.renormalize = bool(params.get("renormalize", False))
+        groups = params.get("groups") or {}
+        self.group_count = int(groups.get("count", 1))
+        self.group_keep = int(groups.get("keep", self.group_count))
+        self.group_top = int(groups.get("top", 2))
+        if self.group_count > 1:
+            if self.scoring != "sigmoid":
+                raise ConfigError("mixture of experts: groups of experts go with sigmoid scoring")
+            if self.experts % self.group_count or not 0 < self.group_keep <= self.group_count \
+                    or self.group_keep * (self.experts // self.group_count) < self.top:
+                raise ConfigError(f"mixture of experts: {self.experts} experts in {self.group_count} groups of which "
+                                  f"{self.group_keep} stay open cannot give {self.top} choices")
+            if self.experts // self.group_count > 64:
+                raise ConfigError("mixture of experts: a group of more than 64 experts is beyond the routing kernel")
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
         self.router: Optional[torch.Tensor] = None
@@ -104,7 +126,11 @@ class MixtureOfExperts(FeedForward):
         ids = torch.empty((n, self.top), dtype=torch.int32, device=dev)
         wts = torch.empty((n, self.top), dtype=torch.float32, device=dev)
         gate = torch.empty((n, self.experts), dtype=torch.float32, device=dev)
-        core.moe_route(logits, self.router_bias, self.top, ids, wts, gate)
+        if self.scoring == "sigmoid":
+            core.moe_route_scored(logits, self.router_bias, self.top, ids, wts, gate, groups=self.group_count,
+                                  keep=self.group_keep, group_top=self.group_top, renorm=self.renormalize)
+        else:
+            core.moe_route(logits, self.router_bias, self.top, ids, wts, gate)
         return ids, wts, gate
 
     def forward(self, x: torch.Tensor, ctx=None) -> torch.Tensor:

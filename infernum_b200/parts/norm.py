@@ -133,3 +133,66 @@ class LayerNorm(Norm):
         out = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
         core.scale_add_norm(x, None, self.weight, self.bias, self.eps, out, centred=self.centred)
         return out
+
+
+@NORMS.register("part_rmsnorm")
+class PartRMSNorm(Norm):
+    """RMS norm over ``parts`` equal consecutive parts of the vector: each part is
+    divided by its own ``sqrt(mean(part^2) + eps)`` and the whole multiplied by the
+    weight; 32-bit throughout.
+
+    Two uses.  ``forward(stream, row_idx)``: the norm of the stream's rows (the
+    final norm).  ``add_normed(stream, y, depth)``: for layers that norm a
+    sub-layer's result, not its input: the stream becomes ``x + norm(y)`` - or,
+    with ``depth = (slot, coef)``, that sum is stored as the stream's result
+    ``slot`` and the stream becomes ``sum_{j <= slot} coef[j] results[j]`` - in one
+    kernel, which also writes the stream's rounding to the activation dtype.
+
+    Parameters: ``hidden_size``, ``eps``, ``parts`` (default 1), ``weight``.
+    """
+
+    def __init__(self, params, rt: Runtime):
+        super().__init__(params, rt)
+        self.hidden_size = int(params["hidden_size"])
+        self.eps = float(params["eps"])
+        self.parts = int(params.get("parts", 1))
+        self.weight_name = params["weight"]
+        self.weight: Optional[torch.Tensor] = None
+        self._stored_bytes = 0
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.weight_name: WeightSpec((self.hidden_size,), init="norm")}
+
+    def bind(self, weights) -> None:
+        w = weights[self.weight_name]
+        self._stored_bytes = w.numel() * w.element_size()
+        self.weight = w.to(torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return self._stored_bytes
+
+    def forward(self, stream: ResidualStream, row_idx: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if stream.pending is not None:
+            stream.flush()
+        residual = stream.residual
+        n_out = residual.shape[0] if row_idx is None else row_idx.numel()
+        out = torch.empty((n_out, self.hidden_size), dtype=self.rt.dtype, device=residual.device)
+        core.part_rmsnorm(residual, self.weight, self.parts, self.eps, out, row_idx=row_idx)
+        return out
+
+    def add_normed(self, stream: ResidualStream, y: torch.Tensor, depth=None) -> None:
+        x = stream.residual
+        results = stream.results if depth is not None else None
+        # (the embedding's output is also result 0: it is never written over)
+        aliases = stream.results is not None and x.data_ptr() == stream.results.data_ptr()
+        out = torch.empty_like(x) if aliases else x
+        act = None if self.rt.is_fp32 else torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+        slot, coef = depth if depth is not None else (0, None)
+        core.sub_norm_add(x, y, self.weight, self.parts, self.eps, out, act, results=results, slot=slot, coef=coef)
+        stream.residual = out
+        stream.act = out if act is None else act
+
+    def apply(self, x: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+        core.part_rmsnorm(x, self.weight, self.parts, self.eps, out)
+        return out

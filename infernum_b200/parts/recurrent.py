@@ -27,6 +27,20 @@ Tensors: ``in`` [2 inner + 2 groups state + heads, hidden], ``conv`` [channels,
 taps], ``conv.b``, ``dt_bias``, ``A_log``, ``D`` [heads], ``norm`` [inner], ``o``
 [hidden, inner].
 
+``delta``: a gated delta rule.  ``q = W_q h`` and ``k = W_k h`` (kv_heads x dim), ``v =
+W_v h`` (heads x vdim); value head a uses key head ``a // (heads / kv_heads)``.  Each of
+q, k, v passes a causal convolution per channel (no bias) and SiLU; q and k are then
+scaled to unit length per head (``x / sqrt(sum x^2 + 1e-6)``), q also by ``dim ** -0.5``.
+``beta = sigmoid(W_b h)`` and ``g = exp(-exp(A_log) softplus(W_a h + dt_bias))`` per head.
+Per head ``S <- g S``, ``u = beta (v - S^T k)``, ``S <- S + k u^T``, ``o = S^T q`` (``S`` is
+dim x vdim); ``o`` is divided by its root mean square per head, multiplied by ``norm``
+(vdim values shared by the heads) and by ``silu(W_g h)``, and projected by ``W_o``.
+Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``vdim``,
+``conv`` (taps; 0 or None: no convolution), ``eps``, ``prefix``.
+Tensors: ``q, k`` [kv_heads*dim, hidden], ``v, g`` [heads*vdim, hidden], ``b, a`` [heads,
+hidden], ``q.conv, k.conv, v.conv`` [channels, taps], ``A_log, dt_bias`` [heads], ``norm``
+[vdim], ``o`` [hidden, heads*vdim].
+
 The state tensor of a slot is flat float32: the heads' matrices, then what the
 shift or the convolution needs of earlier tokens.
 """
@@ -190,3 +204,77 @@ class SsdMixer(Mixer):
         out = torch.empty((N, self.inner), dtype=x.dtype, device=x.device)
         core.gated_group_norm(y, z, self.norm, self.norm_groups, self.eps, out)
         return self.w_o(out)
+
+
+@MIXERS.register("delta")
+class DeltaMixer(Mixer):
+    def __init__(self, params, rt: Runtime):
+        super().__init__(params, rt)
+        self.hidden_size = int(params["hidden_size"])
+        self.heads = int(params["num_heads"])
+        self.kv_heads = int(params.get("num_kv_heads") or self.heads)
+        self.dim = int(params["head_dim"])
+        self.vdim = int(params.get("vdim") or self.dim)
+        self.taps = int(params.get("conv") or 0)
+        self.eps = float(params["eps"])
+        self.prefix = params.get("prefix", "")
+        if self.heads % self.kv_heads:
+            raise ConfigError(f"delta: {self.heads} heads are not a multiple of {self.kv_heads} key heads")
+        if self.dim > scan_ops.MAX_ROWS:
+            raise ConfigError(f"delta: a key of {self.dim} channels is beyond {scan_ops.MAX_ROWS}")
+        if not 0 <= self.taps <= 16:
+            raise ConfigError(f"delta: a convolution of {self.taps} taps is outside 0..16")
+        self.qk = self.kv_heads * self.dim
+        self.inner = self.heads * self.vdim
+        self.channels = 2 * self.qk + self.inner  # q | k | v: what the convolution runs over
+        # rows of the one input product: q | k | v | gate | b | a
+        self.off_gate = self.channels
+        self.off_b = self.channels + self.inner
+        self.off_a = self.off_b + self.heads
+        self.in_rows = self.off_a + self.heads
+        self.state_floats = self.heads * self.dim * self.vdim
+        self.off_conv = self.state_floats  # the convolution's last taps-1 inputs, behind the matrices
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return StateSpec((self.state_floats + max(self.taps - 1, 1) * self.channels,), torch.float32)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        p, D = self.prefix, self.hidden_size
+        specs = {
+            p + "q": WeightSpec((self.qk, D)), p + "k": WeightSpec((self.qk, D)), p + "v": WeightSpec((self.inner, D)),
+            p + "g": WeightSpec((self.inner, D)), p + "b": WeightSpec((self.heads, D)),
+            p + "a": WeightSpec((self.heads, D)),
+            p + "A_log": WeightSpec((self.heads,), init="normal", std=0.5),
+            p + "dt_bias": WeightSpec((self.heads,), init="normal", std=0.5),
+            p + "norm": WeightSpec((self.vdim,), init="norm"),
+            p + "o": WeightSpec((D, self.inner)),
+        }
+        if self.taps:
+            for name, rows in (("q", self.qk), ("k", self.qk), ("v", self.inner)):
+                specs[p + name + ".conv"] = WeightSpec((rows, self.taps), init="normal", std=0.4)
+        return specs
+
+    def bind(self, weights) -> None:
+        p = self.prefix
+        mats = [weights[p + n] for n in ("q", "k", "v", "g", "b", "a")]
+        if len({m.dtype for m in mats}) != 1:
+            raise ConfigError(f"{p}: the input projections are stored in different dtypes")
+        self.w_in = Linear(torch.cat(mats, dim=0), self.rt)
+        self.w_o = Linear(weights[p + "o"], self.rt)
+        self.conv_w = _f32(torch.cat([weights[p + n + ".conv"] for n in ("q", "k", "v")], dim=0)) if self.taps else None
+        self.a_log = _f32(weights[p + "A_log"])
+        self.dt_bias = _f32(weights[p + "dt_bias"])
+        self.norm = _f32(weights[p + "norm"]).repeat(self.heads)  # the heads share one weight
+
+    def weight_bytes(self) -> int:
+        return self.w_in.nbytes + self.w_o.nbytes
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+        N = x.shape[0]
+        proj = self.w_in(x)
+        o = torch.empty((N, self.inner), dtype=torch.float32, device=x.device)
+        scan_ops.delta_scan(proj, 0, self.off_b, self.off_a, self.conv_w, self.a_log, self.dt_bias, cache.state, 0,
+                            self.off_conv, ctx, o, self.heads, self.kv_heads, self.dim, self.vdim, self.rt)
+        y = torch.empty((N, self.inner), dtype=x.dtype, device=x.device)
+        core.head_norm_gate(o, proj[:, self.off_gate: self.off_gate + self.inner], self.norm, self.heads, self.eps, y)
+        return self.w_o(y)

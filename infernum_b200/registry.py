@@ -68,3 +68,5 @@ def _ensure_builtin() -> None:
         from .models import rugesun  # noqa: F401
     if "Nadozen" not in _ARCHITECTURES:
         from .models import nadozen  # noqa: F401
+    if "Bolovik" not in _ARCHITECTURES:
+        from .models import bolovik  # noqa: F401
