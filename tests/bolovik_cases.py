@@ -1,0 +1,130 @@
+"""Small Bolovik configurations for the tests and their model folders."""
+
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+
+def delta(heads, kv_heads, dim, vdim, conv, mlp=None):
+    return {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv},
+            "mlp": mlp}
+
+
+def attention(heads, kv_heads, dim, vdim, scale, window=None, keep_first=None, rot=None, mlp=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if window is not None:
+        m["mask"] = {"size": window}
+        if keep_first is not None:
+            m["mask"]["keep_first"] = keep_first
+    if rot is not None:
+        m["rot"] = rot
+    return {"type": "attention", "mixer": m, "mlp": mlp}
+
+
+def rot(dims, base, scaling=None):
+    r = {"dims": dims, "base": base}
+    if scaling is not None:
+        r["scaling"] = dict(zip(("factor", "low", "high", "original"), scaling))
+    return r
+
+
+DENSE = lambda ff: {"kind": "dense", "ff": ff}  # noqa: E731
+
+
+def moe(ff, experts, top, groups=None):
+    router = {"experts": experts, "top": top}
+    if groups is not None:
+        router["groups"] = {"count": groups[0], "keep": groups[1]}
+    return {"kind": "moe", "expert": {"ff": ff}, "router": router}
+
+
+# Three norm parts; every mixer and feed-forward kind; grouped heads; values narrower and wider
+# than keys; a window that is no multiple of a page, with kept first tokens that end inside a
+# page; all three bands of the frequency scaling; a layer without a feed-forward.
+CASE_A = {
+    "architecture": "Bolovik", "vocab": 211, "width": 96, "norm": {"eps": 1e-5, "groups": 3},
+    "layers": [
+        delta(4, 2, 16, 24, 4, DENSE(72)),
+        attention(6, 2, 16, 8, 0.35, 21, 5, rot(8, 10000.0, (8.0, 1.0, 4.0, 64)), moe(40, 8, 3, (4, 2))),
+        delta(2, 2, 20, 12, 3, None),
+        attention(4, 4, 8, 20, 0.5, 10, 3, rot(8, 100.0), moe(24, 6, 2, (2, 1))),
+        delta(6, 3, 8, 16, 2, moe(16, 5, 2)),
+    ],
+}
+# Values that are 1 or equal, and keys that a model may leave out: one norm part; one head; as
+# many key heads as heads; convolutions of one tap and none; a window of one token; kept first
+# tokens that outnumber the window; no mask; no rotation, and one over the whole head; one expert
+# of one chosen, all experts chosen, one group; sizes that are no multiple of 8.
+CASE_B = {
+    "architecture": "Bolovik", "vocab": 130, "width": 72, "norm": {"eps": 1e-6},
+    "layers": [
+        attention(1, 1, 12, 12, 0.4, 1, 4, rot(12, 50.0), DENSE(40)),
+        delta(1, 1, 28, 10, 1, moe(20, 1, 1)),
+        attention(3, 3, 10, 6, 0.3, None, None, None, moe(12, 3, 3, (1, 1))),
+        {"type": "delta", "mixer": {"heads": 2, "dim": 12}, "mlp": None},
+        attention(2, 1, 6, 14, 0.6, 6, 9, rot(2, 7.0, (2.0, 1.0, 2.0, 16)), None),
+        attention(2, 2, 8, 8, 0.5, 7, 0, None, DENSE(36)),
+    ],
+}
+# Sizes the tensor-core kernels take (head sizes that are multiples of 16, keys and values
+# alike, pages of 16): a window without kept tokens, one with them, attention without a mask; a
+# delta rule with 128 state rows.
+CASE_C = {
+    "architecture": "Bolovik", "vocab": 384, "width": 128, "norm": {"eps": 1e-6, "groups": 2},
+    "layers": [
+        attention(8, 2, 32, 32, 0.2, 45, None, rot(16, 10000.0), DENSE(192)),
+        delta(4, 2, 64, 32, 4, moe(64, 8, 2, (4, 2))),
+        attention(4, 4, 64, 64, 0.15, 40, 17, rot(64, 500000.0, (4.0, 1.0, 4.0, 128)), None),
+        delta(2, 1, 128, 16, 3, DENSE(96)),
+        attention(4, 1, 64, 64, 0.15, None, None, rot(32, 10000.0), moe(32, 4, 2)),
+    ],
+}
+# One layer of each mixer alone, without feed-forwards: what the mixers and the depth average do.
+CASE_D = {
+    "architecture": "Bolovik", "vocab": 97, "width": 64, "norm": {"eps": 1e-5, "groups": 4},
+    "layers": [delta(2, 1, 32, 24, 3, None), attention(4, 2, 16, 12, 0.3, 9, 2, rot(8, 1000.0), None)],
+}
+CASES = {"A": CASE_A, "B": CASE_B, "C": CASE_C, "D": CASE_D}
+PAGE_SIZES = {"A": 4, "B": 8, "C": 16, "D": 4}
+
+
+def make_folder(folder: str, config: dict, seed: int, sharpen: float = 0.0, drop: Optional[list] = None) -> str:
+    """A random model through the package's writer, reshaped so that faults show: slow
+    decays (a state lost or mixed up matters many tokens later), write strengths and decays
+    that vary with the token, projections large beside their biases, and a depth average
+    that mostly hands on the newest result.  ``sharpen`` multiplies the attention layers'
+    ``scale`` so that the softmax is peaked and one wrong key shows in the logits (queries
+    and keys are normed, so scaling a projection would not)."""
+    import json
+
+    from infernum_b200.weights.random_init import write_random_model
+    from safetensors.torch import load_file, save_file
+
+    if sharpen:
+        config = json.loads(json.dumps(config))
+        for layer in config["layers"]:
+            if layer["type"] == "attention":
+                layer["mixer"]["scale"] = layer["mixer"]["scale"] * sharpen
+    write_random_model(folder, config, seed)
+    path = os.path.join(folder, "model.safetensors")
+    tensors = load_file(path)
+    for name in list(tensors):
+        t = tensors[name].float()
+        if name.endswith(".A_log"):
+            t = t - 2.5
+        elif name.endswith((".mix.a", ".mix.b")):
+            t = t * 20.0
+        elif name.endswith((".mix.q", ".mix.k", ".mix.v", ".mix.g", ".gate", ".up", "embed")):
+            t = t * 6.0
+        elif name.endswith(".dwa"):
+            t[-1] += 1.0
+        else:
+            continue
+        tensors[name] = t.to(torch.bfloat16)
+    for name in drop or []:
+        del tensors[name]
+    save_file(tensors, path, metadata={"format": "pt"})
+    return folder

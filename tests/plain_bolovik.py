@@ -90,11 +90,17 @@ def delta_rule(q, k, v, beta, g):
 
 def delta_mixer(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float):
     dt = h.dtype
-    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, dk = m["heads"], m["dim"]
+    G, dv = m.get("kv_heads", H), m.get("vdim", dk)
     T = h.shape[0]
-    q = silu(causal_conv(h @ _t(W[p + "q"], dt).t(), _t(W[p + "q.conv"], dt))).reshape(T, G, dk)
-    k = silu(causal_conv(h @ _t(W[p + "k"], dt).t(), _t(W[p + "k.conv"], dt))).reshape(T, G, dk)
-    v = silu(causal_conv(h @ _t(W[p + "v"], dt).t(), _t(W[p + "v.conv"], dt))).reshape(T, H, dv)
+
+    def conv_act(name):
+        z = h @ _t(W[p + name], dt).t()
+        if m.get("conv"):
+            z = causal_conv(z, _t(W[p + name + ".conv"], dt))
+        return silu(z)
+
+    q, k, v = conv_act("q").reshape(T, G, dk), conv_act("k").reshape(T, G, dk), conv_act("v").reshape(T, H, dv)
     q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
     k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
     beta = torch.sigmoid(h @ _t(W[p + "b"], dt).t())  # [T, H]
@@ -152,7 +158,8 @@ def visible(T: int, size: int, keep_first: int) -> torch.Tensor:
 
 def attention_mixer(h, W, p: str, m: dict, eps: float):
     dt = h.dtype
-    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, dk = m["heads"], m["dim"]
+    G, dv = m.get("kv_heads", H), m.get("vdim", dk)
     T = h.shape[0]
     q = (h @ _t(W[p + "q"], dt).t() + _t(W[p + "q.b"], dt)).reshape(T, H, dk)
     k = (h @ _t(W[p + "k"], dt).t() + _t(W[p + "k.b"], dt)).reshape(T, G, dk)
@@ -171,7 +178,7 @@ def attention_mixer(h, W, p: str, m: dict, eps: float):
     per = H // G
     outs = []
     for hd in range(H):
-        s = (q[:, hd] @ k[:, hd // per].t()) * float(m["scale"])
+        s = (q[:, hd] @ k[:, hd // per].t()) * float(m.get("scale", dk ** -0.5))
         s = s.masked_fill(~see, float("-inf"))
         outs.append(torch.softmax(s, dim=-1) @ v[:, hd // per])
     return torch.cat(outs, dim=-1) @ _t(W[p + "o"], dt).t()
@@ -192,7 +199,8 @@ def route(h, router_w, r: dict):
     groups = r.get("groups")
     allowed = torch.ones_like(s, dtype=torch.bool)
     if groups:
-        n, keep = int(groups["count"]), int(groups["keep"])
+        n = int(groups["count"])
+        keep = int(groups.get("keep", n))
         per = E // n
         sg = s.reshape(-1, n, per)
         gscore = sg.topk(min(2, per), dim=-1).values.sum(-1)  # [T, n]
@@ -244,3 +252,41 @@ def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens, dtype=torch.float64, 
     if return_layers:
         return logits, torch.stack(after)
     return logits
+
+
+def argmax(logits) -> int:
+    return int(torch.argmax(logits).item())
+
+
+def read_config(folder_or_dict) -> dict:
+    import json
+    import os
+
+    if isinstance(folder_or_dict, dict):
+        return folder_or_dict
+    with open(os.path.join(folder_or_dict, "config.json")) as fh:
+        return json.load(fh)
+
+
+def read_weights(folder: str) -> Dict[str, torch.Tensor]:
+    import os
+
+    from safetensors.torch import load_file
+
+    return {k: (v.to(torch.float64) if v.is_floating_point() else v) for k, v in
+            load_file(os.path.join(folder, "model.safetensors")).items()}
+
+
+class Plain:
+    """The plain implementation over a model folder, logits cached by sequence."""
+
+    def __init__(self, folder: Optional[str], config: Optional[dict] = None, weights=None):
+        self.cfg = read_config(folder if folder is not None else config)
+        self.weights = read_weights(folder) if folder is not None else weights
+        self._cache: Dict[tuple, torch.Tensor] = {}
+
+    def logits(self, tokens) -> torch.Tensor:
+        key = tuple(tokens)
+        if key not in self._cache:
+            self._cache[key] = forward(self.cfg, self.weights, list(tokens))
+        return self._cache[key]
