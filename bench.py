@@ -392,6 +392,49 @@ def nadozen_prefill_flops(cfg: dict, T: int) -> float:
     return total + 2.0 * D * cfg["vocab"]
 
 
+def bolovik_config(width, layers, heads, kv_heads, ff, vocab, window=4096, keep_first=4, experts=16, top=4):
+    """Layers in pairs: sliding-window attention that keeps the first tokens (heads of 128, half of
+    each rotated) with a gated GELU feed-forward, then a gated delta rule (value heads of 128 over
+    half as many key heads, a convolution of 4 taps) with a mixture of experts whose chosen experts
+    do a dense layer's work (an expert has ff / top columns; four groups of which two stay open)."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+           "mask": {"size": window, "keep_first": keep_first},
+           "rot": {"dims": 64, "base": 500000.0,
+                   "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    dh = width // 128
+    delta = {"heads": dh, "kv_heads": max(1, dh // 2), "dim": 128, "vdim": 128, "conv": 4}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // top},
+           "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}}
+    out = [{"type": "attention", "mixer": att, "mlp": dense} if i % 2 == 0 else
+           {"type": "delta", "mixer": delta, "mlp": moe} for i in range(layers)]
+    return {"architecture": "Bolovik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6, "groups": 4},
+            "layers": out, "max_position": 8192}
+
+
+def bolovik_prefill_flops(cfg: dict, T: int) -> float:
+    """Multiply-adds x 2 of one prompt step: the products (a token's chosen experts only), the
+    attention over the keys each query sees, and the delta rule's two reads and one write of its
+    state per token."""
+    D, total = cfg["width"], 0.0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        H, G, d, v = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        if layer["type"] == "delta":
+            total += 2.0 * T * D * (2 * G * d + 2 * H * v + 2 * H) + 2.0 * T * H * v * D + 2.0 * T * H * d * v * 3
+        else:
+            mask = m.get("mask") or {}
+            w, keep = mask.get("size", 0), mask.get("keep_first", 0)
+            keys = sum(min(t + 1, w + min(keep, max(0, t + 1 - w))) if w else t + 1 for t in range(T))
+            total += 2.0 * T * D * (H * d + G * d + G * v) + 2.0 * T * H * v * D + 2.0 * H * (d + v) * keys
+        mlp = layer.get("mlp")
+        if mlp and mlp["kind"] == "dense":
+            total += 6.0 * T * D * mlp["ff"]
+        elif mlp:
+            total += 6.0 * T * D * mlp["expert"]["ff"] * mlp["router"]["top"] + 2.0 * T * D * mlp["router"]["experts"]
+    return total + 2.0 * D * cfg["vocab"]
+
+
 DESIGN_SIZES = {
     # name: (width, layers, heads, feed-forward, vocabulary, q_rank, llama kv heads)
     "2b-shape": (2048, 8, 16, 8192, 32000, 768, 4),
@@ -400,8 +443,10 @@ DESIGN_SIZES = {
 
 
 def design_compare(args, peaks) -> dict:
-    """Prefill and decode of the chosen design at a few sizes, and of the Llama decoder at
-    the same width, depth, heads, feed-forward width and vocabulary."""
+    """Prefill and decode of the chosen design at a few sizes, and of the decoder it is set beside
+    (the Llama decoder; for Bolovik the Nadozen decoder, whose layers also alternate window
+    attention and a recurrent state) at the same width, depth, heads, feed-forward width and
+    vocabulary."""
     import gc
 
     import torch
@@ -419,19 +464,29 @@ def design_compare(args, peaks) -> dict:
                  "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": 128,
                  "intermediate_size": ff, "vocab_size": vocab, "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
                  "tie_word_embeddings": False, "max_position_embeddings": 8192}
+        beside, beside_cfg, beside_flops = "llama", llama, None
         if args.design == "nadozen":
             other = nadozen_config(width, layers, heads, kv_heads, ff, vocab)
             other_flops = nadozen_prefill_flops
+        elif args.design == "bolovik":
+            other = bolovik_config(width, layers, heads, kv_heads, ff, vocab)
+            other_flops = bolovik_prefill_flops
+            beside, beside_cfg, beside_flops = "nadozen", nadozen_config(width, layers, heads, kv_heads, ff, vocab), \
+                nadozen_prefill_flops
         else:
             other = rugesun_config(width, layers, heads, ff, vocab, q_rank)
             other_flops = rugesun_prefill_flops
-        for label, cfg in ((args.design, other), ("llama", llama)):
+        for label, cfg in ((args.design, other), (beside, beside_cfg)):
             if args.only_model and label != args.only_model:
                 continue
             model = ib.random_model(cfg, seed=args.seed, dtype="bfloat16", device="cuda:0", options=dict(opts))
             row = {}
-            flops = (lambda T, c=cfg: other_flops(c, T)) if label != "llama" else \
-                (lambda T, c=cfg: prefill_flops(c, T, layers))
+            if label == args.design:
+                flops = lambda T, c=cfg: other_flops(c, T)  # noqa: E731
+            elif beside_flops is not None:
+                flops = lambda T, c=cfg: beside_flops(c, T)  # noqa: E731
+            else:
+                flops = lambda T, c=cfg: prefill_flops(c, T, layers)  # noqa: E731
             for T in (512, 2048):
                 if args.only == "decode":
                     break
@@ -537,11 +592,11 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print its numbers (for profiling)")
     ap.add_argument("--no-cuda-graph", action="store_true", help="launch decode steps kernel by kernel")
-    ap.add_argument("--design", choices=["rugesun", "nadozen"], default=None,
+    ap.add_argument("--design", choices=["rugesun", "nadozen", "bolovik"], default=None,
                     help="instead of the default workload: prefill and decode of this design at a few sizes,\n"
-                         "beside the Llama decoder at equal sizes; prints one JSON line {\"design\": ...}")
+                         "beside the Llama decoder (bolovik: the Nadozen decoder) at equal sizes; prints one JSON line {\"design\": ...}")
     ap.add_argument("--size", default=None, help="with --design: one of its sizes only")
-    ap.add_argument("--only-model", default=None, help="with --design: the design's name or 'llama' only")
+    ap.add_argument("--only-model", default=None, help="with --design: the design's name, or the name of the one beside it, only")
     args = ap.parse_args()
 
     if args.impl == "reference":

@@ -64,6 +64,7 @@ struct Params {
     unsigned* err;
     const float* sink;  // optional [nh]: a logit per head that joins the softmax's denominator only
     int q_stride, out_stride, max_blocks, nh, nkv, page_size, num_pages, window;
+    int keep_first;   // behind a window: keys at positions below this stay visible (0 without a window)
     int gs;           // tile mode: query heads of one kv head handled together (<= 16)
     int n_hsub;       // tile mode: ceil((nh / nkv) / gs)
     int gs_split;     // split mode: the same with at most 8
@@ -173,9 +174,19 @@ __device__ __forceinline__ void locate_tile(TileRows& tr, const Params& p, const
     }
 }
 
-// Copies one tile into a stage.  Rows outside [kv_min, kv_hi) - pages below
-// kv_min may already have been given back by a window - and rows whose
-// block-table entry is not a page of the pool are zero-filled.
+// The key tiles of a range of queries behind a window that keeps the first tokens: first
+// the tiles that hold kept tokens and lie wholly below the window's first tile (kv_lo, a
+// multiple of BN), then the window's own.  Without kept tokens there are none of the former.
+__device__ __forceinline__ int keep_tiles(const Params& p, int kv_lo) {
+    return p.keep_first > 0 ? (min(p.keep_first, kv_lo) + BN - 1) / BN : 0;
+}
+__device__ __forceinline__ int tile_start_of(int t, int n_keep, int kv_lo) {
+    return t < n_keep ? t * BN : kv_lo + (t - n_keep) * BN;
+}
+
+// Copies one tile into a stage.  Rows outside [kv_min, kv_hi) that are not kept first
+// tokens - pages below kv_min may already have been given back by a window - and rows
+// whose block-table entry is not a page of the pool are zero-filled.
 __device__ __forceinline__ void copy_tile(bf16* ks, bf16* vs, const Params& p, const TileRows& tr,
                                           int g, int kv_min, int kv_hi) {
 #pragma unroll
@@ -186,7 +197,7 @@ __device__ __forceinline__ void copy_tile(bf16* ks, bf16* vs, const Params& p, c
         const int j = tr.tile_start + row;
         const int slot = p.page_shift >= 0 ? (j & (p.page_size - 1)) : (j % p.page_size);
         const int page = tr.page[i];
-        const bool in_range = j >= kv_min && j < kv_hi;
+        const bool in_range = (j >= kv_min || j < p.keep_first) && j < kv_hi;
         const bool ok = in_range && page >= 0 && page < p.num_pages;
         if (in_range && !ok) atomicOr(p.err, IB_FLAG_BAD_PAGE);
         const size_t src =
@@ -242,7 +253,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_tile_kernel(const Params p
     const int kv_hi = pos0 + r_begin + r_count;  // exclusive
     const int kv_min = p.window > 0 ? max(0, pos0 + r_begin - p.window + 1) : 0;
     const int kv_lo = (kv_min / BN) * BN;
-    const int n_tiles = (kv_hi - kv_lo + BN - 1) / BN;
+    const int n_keep = keep_tiles(p, kv_lo);
+    const int n_tiles = n_keep + (kv_hi - kv_lo + BN - 1) / BN;
     const int t_begin = 0, t_end = n_tiles;
 
     // ---- queries as A fragments, straight from global memory -------------------
@@ -272,21 +284,21 @@ __global__ void __launch_bounds__(NTHREADS) attention_tile_kernel(const Params p
     // sits on the critical path.
     TileRows tr;
     if (t_begin < t_end) {
-        locate_tile(tr, p, table, kv_lo + t_begin * BN);
+        locate_tile(tr, p, table, tile_start_of(t_begin, n_keep, kv_lo));
         copy_tile(k_s[0], v_s[0], p, tr, g, kv_min, kv_hi);
     }
     cp_async_commit();
-    if (t_begin + 1 < t_end) locate_tile(tr, p, table, kv_lo + (t_begin + 1) * BN);
+    if (t_begin + 1 < t_end) locate_tile(tr, p, table, tile_start_of(t_begin + 1, n_keep, kv_lo));
 
     for (int t = t_begin; t < t_end; ++t) {
         const int stage = (t - t_begin) & 1;
         if (t + 1 < t_end) copy_tile(k_s[stage ^ 1], v_s[stage ^ 1], p, tr, g, kv_min, kv_hi);
         cp_async_commit();
-        if (t + 2 < t_end) locate_tile(tr, p, table, kv_lo + (t + 2) * BN);
+        if (t + 2 < t_end) locate_tile(tr, p, table, tile_start_of(t + 2, n_keep, kv_lo));
         cp_async_wait<1>();
         __syncthreads();
 
-        const int tile_start = kv_lo + t * BN;
+        const int tile_start = tile_start_of(t, n_keep, kv_lo);
         const bf16* ks_ = k_s[stage];
         const bf16* vs_ = v_s[stage];
 
@@ -318,7 +330,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_tile_kernel(const Params p
                 for (int i = 0; i < 4; ++i) {
                     const int h = i >> 1;
                     const int key = tile_start + key_base + n * 8 + tig * 2 + (i & 1);
-                    const bool ok = key <= my_pos[h] && (p.window <= 0 || key > my_pos[h] - p.window);
+                    const bool ok = key <= my_pos[h] &&
+                                    (p.window <= 0 || key > my_pos[h] - p.window || key < p.keep_first);
                     const float v = ok ? s[n][i] * p.scale_log2 : -INFINITY;
                     s[n][i] = v;
                     m_new[h] = fmaxf(m_new[h], v);
@@ -541,7 +554,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
     const int kv_hi = pos0 + rows_e;
     const int kv_min = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     const int kv_lo = (kv_min / BN) * BN;
-    const int n_tiles = (kv_hi - kv_lo + BN - 1) / BN;
+    const int n_keep = keep_tiles(p, kv_lo);
+    const int n_tiles = n_keep + (kv_hi - kv_lo + BN - 1) / BN;
     const int per = (n_tiles + p.splits - 1) / p.splits;
     const int t_begin = blockIdx.x * per;
     const int t_end = min(n_tiles, t_begin + per);
@@ -552,13 +566,13 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
 #pragma unroll
     for (int pre = 0; pre < SPLIT_STAGES - 1; ++pre) {
         if (t_begin + pre < t_end) {
-            locate_tile(tr, p, table, kv_lo + (t_begin + pre) * BN);
+            locate_tile(tr, p, table, tile_start_of(t_begin + pre, n_keep, kv_lo));
             copy_tile(k_stage(pre), v_stage(pre), p, tr, g, kv_min, kv_hi);
         }
         cp_async_commit();
     }
     if (t_begin + SPLIT_STAGES - 1 < t_end)
-        locate_tile(tr, p, table, kv_lo + (t_begin + SPLIT_STAGES - 1) * BN);
+        locate_tile(tr, p, table, tile_start_of(t_begin + SPLIT_STAGES - 1, n_keep, kv_lo));
 
     // ---- queries as B fragments (column n = gid), while the first tile flies ----------
     unsigned qf[HD / 16][2];
@@ -596,9 +610,10 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
             copy_tile(k_stage(nst), v_stage(nst), p, tr, g, kv_min, kv_hi);
         }
         cp_async_commit();
-        if (t + SPLIT_STAGES < t_end) locate_tile(tr, p, table, kv_lo + (t + SPLIT_STAGES) * BN);
+        if (t + SPLIT_STAGES < t_end)
+            locate_tile(tr, p, table, tile_start_of(t + SPLIT_STAGES, n_keep, kv_lo));
 
-        const int tile_start = kv_lo + t * BN;
+        const int tile_start = tile_start_of(t, n_keep, kv_lo);
         const bf16* ks_ = k_stage(stage);
         const bf16* vs_ = v_stage(stage);
 
@@ -618,7 +633,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
         for (int i = 0; i < 4; ++i) {
             const int h = i & 1;
             const int key = tile_start + key_base + gid + 8 * (i >> 1);
-            const bool ok = key <= col_pos[h] && (p.window <= 0 || key > col_pos[h] - p.window);
+            const bool ok = key <= col_pos[h] &&
+                            (p.window <= 0 || key > col_pos[h] - p.window || key < p.keep_first);
             sc[i] = ok ? sc[i] * p.scale_log2 : -INFINITY;
             m_new[h] = fmaxf(m_new[h], sc[i]);
         }
@@ -688,8 +704,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_split_kernel(const Params 
 // Whole pages are copied, so rows outside the request's keys hold whatever the
 // page held: their scores are masked, and the warp that owns them clears their
 // V rows in shared memory first (0 x anything must be 0).  Pages outside the
-// key range are not looked up (a window may have given them back); page 0 is
-// fetched in their place.
+// key range - the window's pages and those of the kept first tokens - are not
+// looked up (a window may have given them back); page 0 is fetched in their place.
 // ---------------------------------------------------------------------------
 constexpr int TMA_KB = HD / 64;
 constexpr int TMA_BLOCK_BYTES = BN * 128;                   // 64 rows x 128 bytes
@@ -768,7 +784,8 @@ attention_split_tma_kernel(const Params p, const __grid_constant__ CUtensorMap m
     const int kv_hi = pos0 + rows_e;
     const int kv_min = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     const int kv_lo = (kv_min / BN) * BN;
-    const int n_tiles = (kv_hi - kv_lo + BN - 1) / BN;
+    const int n_keep = keep_tiles(p, kv_lo);
+    const int n_tiles = n_keep + (kv_hi - kv_lo + BN - 1) / BN;
     const int per = (n_tiles + p.splits - 1) / p.splits;
     const int t_begin = blockIdx.x * per;
     const int t_end = min(n_tiles, t_begin + per);
@@ -787,14 +804,16 @@ attention_split_tma_kernel(const Params p, const __grid_constant__ CUtensorMap m
         const int box_rows = p.page_size < BN ? p.page_size : BN;
         const int ppt = BN / box_rows;
         const int first_page = kv_min >> p.page_shift, last_page = (kv_hi - 1) >> p.page_shift;
+        const int kept_page = p.keep_first > 0 ? (p.keep_first - 1) >> p.page_shift : -1;  // the last page of kept tokens
         auto lookup = [&](int t) -> int {
-            const int pi = (kv_lo + t * BN + lane * box_rows) >> p.page_shift;
-            return (lane < ppt && t < t_end && pi >= first_page && pi <= last_page && pi < p.max_blocks)
+            const int pi = (tile_start_of(t, n_keep, kv_lo) + lane * box_rows) >> p.page_shift;
+            return (lane < ppt && t < t_end && (pi >= first_page || pi <= kept_page) && pi <= last_page &&
+                    pi < p.max_blocks)
                        ? table[pi] : 0;
         };
         int page_next = lookup(t_begin);
         bool ok = true;
-        const int t_wait = (pos0 - kv_lo) / BN;  // the first tile with a token of this step
+        const int t_wait = n_keep + (pos0 - kv_lo) / BN;  // the first tile with a token of this step
         bool waited = false;
         for (int t = t_begin; t < t_end; ++t) {
             const int i = t - t_begin, st = i % TMA_STAGES;
@@ -812,7 +831,7 @@ attention_split_tma_kernel(const Params p, const __grid_constant__ CUtensorMap m
                     atomicOr(p.err, IB_FLAG_BAD_PAGE);
                     page = 0;
                 }
-                const int key0 = kv_lo + t * BN + lane * box_rows;
+                const int key0 = tile_start_of(t, n_keep, kv_lo) + lane * box_rows;
                 const int y = (page * p.nkv + g) * p.page_size + (key0 & (p.page_size - 1));
                 unsigned char* kd = reinterpret_cast<unsigned char*>(k_stage(st)) + lane * box_rows * 128;
                 unsigned char* vd = reinterpret_cast<unsigned char*>(v_stage(st)) + lane * box_rows * 128;
@@ -852,14 +871,14 @@ attention_split_tma_kernel(const Params p, const __grid_constant__ CUtensorMap m
         for (int t = t_begin; t < t_end; ++t) {
             const int i = t - t_begin, st = i % TMA_STAGES;
             if (!mbar_wait(&full_bar[st], (i / TMA_STAGES) & 1)) { ok = false; break; }
-            const int tile_start = kv_lo + t * BN;
+            const int tile_start = tile_start_of(t, n_keep, kv_lo);
             const bf16* ks_ = k_stage(st);
             bf16* vs_ = v_stage(st);
             if (tile_start < kv_min || tile_start + BN > kv_hi) {
                 // clear the V rows of my keys that are not the request's
                 for (int c = lane; c < 16 * CH; c += 32) {
                     const int row = key_base + c / CH, key = tile_start + row;
-                    if (key < kv_min || key >= kv_hi)
+                    if ((key < kv_min && key >= p.keep_first) || key >= kv_hi)
                         *reinterpret_cast<uint4*>(const_cast<bf16*>(swz(vs_, row, (c % CH) * 8))) =
                             make_uint4(0u, 0u, 0u, 0u);
                 }
@@ -883,7 +902,8 @@ attention_split_tma_kernel(const Params p, const __grid_constant__ CUtensorMap m
             for (int q = 0; q < 4; ++q) {
                 const int h = q & 1;
                 const int key = tile_start + key_base + gid + 8 * (q >> 1);
-                const bool in = key <= col_pos[h] && (p.window <= 0 || key > col_pos[h] - p.window);
+                const bool in = key <= col_pos[h] &&
+                                (p.window <= 0 || key > col_pos[h] - p.window || key < p.keep_first);
                 sc[q] = in ? sc[q] * p.scale_log2 : -INFINITY;
                 m_new[h] = fmaxf(m_new[h], sc[q]);
             }
@@ -1014,7 +1034,7 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
                                void* out, int out_stride, const int* cu_rows, const int* q_start,
                                const int* block_tables, int max_blocks, int n_entries, int n_rows,
                                int max_rows_per_entry, int nh, int nkv, int page_size,
-                               int num_pages, int window, float scale, int mode, int splits,
+                               int num_pages, int window, int keep_first, float scale, int mode, int splits,
                                void* scratch, long long scratch_bytes, const float* sink, unsigned* err,
                                void* stream) {
     if (n_entries <= 0 || n_rows <= 0) return IB_OK;
@@ -1045,6 +1065,7 @@ IB_EXPORT int ib_attention_mma(const void* q, int q_stride, const void* k_pool, 
     p.page_size = page_size;
     p.num_pages = num_pages;
     p.window = window;
+    p.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
     p.page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if ((1 << b) == page_size) p.page_shift = b;

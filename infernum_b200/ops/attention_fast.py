@@ -36,7 +36,7 @@ def lib_for(head_dim: int) -> ctypes.CDLL:
         lib = load_module(f"attn_hd{head_dim}", ["attention_mma.cu"], [f"-DIB_HD={head_dim}"])
         lib.ib_attention_mma.argtypes = [
             _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
-            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+            _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
             _c_float, _c_int, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p]
         lib.ib_attention_mma.restype = _c_int
         lib.ib_attention_mma_scratch_bytes.argtypes = [_c_int, _c_int, _c_int]
@@ -158,8 +158,8 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=No
     num_pages, nkv, page_size, hd = k_pool.shape
     if not supported(hd):
         return False
-    if v_pool.shape[3] != hd or (keep_first > 0 and window > 0):
-        return False  # (values of another size, or kept first tokens behind a window: not in these kernels)
+    if v_pool.shape[3] != hd:
+        return False  # (values of another size than keys: not in these kernels)
     if q.stride(0) % 2 or out.stride(0) % 2 or q.data_ptr() % 4 or out.data_ptr() % 4:
         return False  # (rows of an odd length, as a view of a wider product may have: the plain kernel takes them)
     if sink is not None and (sink.dtype != torch.float32 or sink.numel() != n_heads or not sink.is_contiguous()):
@@ -205,7 +205,7 @@ def run(q, k_pool, v_pool, out, ctx, tables, n_heads, scale, window, rt, sink=No
         q.data_ptr(), q.stride(0), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
         out.stride(0), ctx.cu_rows.data_ptr(), ctx.q_start.data_ptr(), tables.data_ptr(),
         tables.shape[1], ctx.n_entries, ctx.n_rows, ctx.max_rows_per_entry, n_heads, nkv,
-        page_size, num_pages, int(window), float(scale), mode, splits,
+        page_size, num_pages, int(window), int(keep_first) if window > 0 else 0, float(scale), mode, splits,
         scratch_ptr, scratch_bytes, sink.data_ptr() if sink is not None else None, rt.err.data_ptr(),
         core.stream_ptr(q))
     core.check(code, "attention_mma")

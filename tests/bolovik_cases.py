@@ -91,13 +91,15 @@ CASES = {"A": CASE_A, "B": CASE_B, "C": CASE_C, "D": CASE_D}
 PAGE_SIZES = {"A": 4, "B": 8, "C": 16, "D": 4}
 
 
-def make_folder(folder: str, config: dict, seed: int, sharpen: float = 0.0, drop: Optional[list] = None) -> str:
+def make_folder(folder: str, config: dict, seed: int, sharpen: float = 0.0, drop: Optional[list] = None,
+                gain: float = 1.0) -> str:
     """A random model through the package's writer, reshaped so that faults show: slow
     decays (a state lost or mixed up matters many tokens later), write strengths and decays
-    that vary with the token, projections large beside their biases, and a depth average
-    that mostly hands on the newest result.  ``sharpen`` multiplies the attention layers'
+    that vary with the token, projections large beside their biases, router logits of order
+    one, and a depth average that mostly hands on the newest result.  ``sharpen`` multiplies the attention layers'
     ``scale`` so that the softmax is peaked and one wrong key shows in the logits (queries
-    and keys are normed, so scaling a projection would not)."""
+    and keys are normed, so scaling a projection would not).  ``gain`` below 1 scales the
+    projections up less (1 + gain (factor - 1)): their results' rounding is scaled with them."""
     import json
 
     from infernum_b200.weights.random_init import write_random_model
@@ -116,11 +118,13 @@ def make_folder(folder: str, config: dict, seed: int, sharpen: float = 0.0, drop
         if name.endswith(".A_log"):
             t = t - 2.5
         elif name.endswith((".mix.a", ".mix.b")):
-            t = t * 20.0
+            t = t * (1.0 + gain * 19.0)
         elif name.endswith((".mix.q", ".mix.k", ".mix.v", ".mix.g", ".gate", ".up", "embed")):
-            t = t * 6.0
+            t = t * (1.0 + gain * 5.0)
         elif name.endswith(".dwa"):
             t[-1] += 1.0
+        elif name.endswith(".router"):
+            t = t * (2.0 / t.shape[1] ** 0.5)  # logits of order one: scores that are not saturated
         else:
             continue
         tensors[name] = t.to(torch.bfloat16)

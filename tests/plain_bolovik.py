@@ -213,6 +213,39 @@ def route(h, router_w, r: dict):
     return ids, torch.gather(s, 1, ids)
 
 
+def routing_margin(h, router_w, r: dict) -> torch.Tensor:
+    """[T]: how far each token's routing is from going another way - the gap between
+    the last chosen score and the best one left out among the open groups, and between
+    the last open group's score and the best closed one - in units of the scores' spread
+    (infinite where nothing is left out).  A small margin means that rounding may choose
+    otherwise, with an equally valid result."""
+    E, top = int(r["experts"]), int(r["top"])
+    s = torch.sigmoid(h @ router_w.t())
+    T = s.shape[0]
+    spread = (s.max(-1).values - s.min(-1).values).clamp_min(1e-9)
+    margin = torch.full((T,), float("inf"), dtype=s.dtype)
+    groups = r.get("groups")
+    allowed = torch.ones_like(s, dtype=torch.bool)
+    if groups:
+        n = int(groups["count"])
+        keep = int(groups.get("keep", n))
+        per = E // n
+        gscore = s.reshape(T, n, per).topk(min(2, per), dim=-1).values.sum(-1)
+        order = gscore.sort(dim=-1, descending=True)
+        if keep < n:
+            margin = torch.minimum(margin, (order.values[:, keep - 1] - order.values[:, keep]) / spread)
+        gm = torch.zeros_like(gscore, dtype=torch.bool)
+        gm.scatter_(1, order.indices[:, :keep], True)
+        allowed = gm[:, :, None].expand(-1, -1, per).reshape(T, E)
+    masked = torch.where(allowed, s, torch.full_like(s, -1.0))
+    order = masked.sort(dim=-1, descending=True).values
+    if top < E:
+        gap = torch.where(order[:, top] >= 0, (order[:, top - 1] - order[:, top]) / spread,
+                          torch.full_like(spread, float("inf")))
+        margin = torch.minimum(margin, gap)
+    return margin
+
+
 def moe_ff(h, W, p: str, mlp: dict):
     dt = h.dtype
     ids, wts = route(h, _t(W[p + "router"], dt), mlp["router"])
@@ -225,9 +258,11 @@ def moe_ff(h, W, p: str, mlp: dict):
     return out
 
 
-def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens, dtype=torch.float64, return_layers: bool = False):
+def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens, dtype=torch.float64, return_layers: bool = False,
+            margins_out: Optional[list] = None):
     """Logits [T, vocab] of one whole sequence (and, on request, the stream after
-    every layer [layers, T, width])."""
+    every layer [layers, T, width]); ``margins_out`` collects the routing margins [T]
+    of every mixture of experts."""
     eps, parts = float(cfg["norm"]["eps"]), int(cfg["norm"].get("groups", 1))
     x = _t(W["embed"], dtype)[torch.as_tensor(tokens, dtype=torch.long)]
     results = [x]
@@ -244,6 +279,8 @@ def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens, dtype=torch.float64, 
         mlp = layer.get("mlp")
         if mlp is not None:
             y = dense_ff(x, W, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(x, W, p + "mlp.", mlp)
+            if mlp["kind"] != "dense" and margins_out is not None:
+                margins_out.append(routing_margin(x, _t(W[p + "mlp.router"], dtype), mlp["router"]))
             x = x + part_rms_norm(y, _t(W[p + "norm2"], dtype), parts, eps)
         results.append(x)
         x = depth_mix(results, _t(W[p + "dwa"], dtype))
@@ -284,9 +321,18 @@ class Plain:
         self.cfg = read_config(folder if folder is not None else config)
         self.weights = read_weights(folder) if folder is not None else weights
         self._cache: Dict[tuple, torch.Tensor] = {}
+        self._margins: Dict[tuple, torch.Tensor] = {}
 
     def logits(self, tokens) -> torch.Tensor:
         key = tuple(tokens)
         if key not in self._cache:
-            self._cache[key] = forward(self.cfg, self.weights, list(tokens))
+            margins: list = []
+            self._cache[key] = forward(self.cfg, self.weights, list(tokens), margins_out=margins).to(torch.float32)
+            self._margins[key] = torch.stack(margins).min(0).values if margins else \
+                torch.full((len(key),), float("inf"))
         return self._cache[key]
+
+    def margins(self, tokens) -> torch.Tensor:
+        """Per position the smallest routing margin over the layers."""
+        self.logits(tokens)
+        return self._margins[tuple(tokens)]
