@@ -173,6 +173,8 @@ struct Params {
     unsigned* err;
     int T, N, K, ldo;
     int act;  // with the gated epilogue: 1 = SiLU, 2 = GELU (tanh form)
+    const float* scale;   // with the gated epilogue, optional [T, n_scales]: out[t, c] *= scale[t, c / cols_per_scale]
+    int n_scales, cols_per_scale;   // (experts side by side and the weight a token's router gave each; 16 | cols_per_scale)
     int t_tiles;   // token tiles of 256
     int t_group;   // token tiles of a group: the first region is walked group by group
     int tiles;     // all tiles
@@ -339,9 +341,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                         tmem_ld16(taddr + blk * 128 + 64 + c, u);
                         tmem_ld_wait();
                         float v[16];
+                        const int col = n0 / 2 + blk * 64 + c;
+                        // (sixteen columns share a scale; those past the row's end are not stored)
+                        const float sc = p.scale && live && col < limit
+                                             ? p.scale[(size_t)gt * p.n_scales + col / p.cols_per_scale] : 1.f;
 #pragma unroll
-                        for (int q = 0; q < 16; ++q) v[q] = gate_times(__uint_as_float(g[q]), __uint_as_float(u[q]), p.act);
-                        if (live) store16(row, n0 / 2 + blk * 64 + c, limit, v);
+                        for (int q = 0; q < 16; ++q)
+                            v[q] = gate_times(__uint_as_float(g[q]), __uint_as_float(u[q]), p.act) * sc;
+                        if (live) store16(row, col, limit, v);
                     }
                 }
             } else {
@@ -448,10 +455,14 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap&
 // that walk over them.  The weight rows are cut into `cols_a` columns of `bn_a`
 // rows and the rest into columns of `bn_b` rows (multiples of 16 from 32 to 256; of
 // 128 with `swiglu`).
-IB_EXPORT int ib_gemm_pair(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int T, int N,
-                           int K, int swiglu, int bn_a, int cols_a, int bn_b, int t_group, int sm_count,
-                           unsigned* err, void* stream) {
+// `scale` (with `swiglu` only; float32 [T, (N/2) / cols_per_scale], or null): every output is also
+// multiplied by scale[t, column / cols_per_scale] (cols_per_scale a multiple of 16 that divides N/2).
+IB_EXPORT int ib_gemm_pair_scaled(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int T, int N,
+                                  int K, int swiglu, int bn_a, int cols_a, int bn_b, int t_group, int sm_count,
+                                  const float* scale, int cols_per_scale, unsigned* err, void* stream) {
     if (T <= 0 || N <= 0) return IB_OK;
+    if (scale && (!swiglu || cols_per_scale <= 0 || cols_per_scale % 16 || (N / 2) % cols_per_scale))
+        return IB_ERR_BAD_ARG;
     if (!x || !w || !out || !err || K <= 0 || sm_count < 2 || cols_a < 0) return IB_ERR_BAD_ARG;
     const int out_cols = swiglu ? N / 2 : N;
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || (ldx % 8) || (ldw % 8) ||
@@ -467,6 +478,9 @@ IB_EXPORT int ib_gemm_pair(const void* x, int ldx, const void* w, int ldw, void*
     p.K = K;
     p.ldo = ldo;
     p.act = swiglu;
+    p.scale = scale;
+    p.cols_per_scale = scale ? cols_per_scale : 1;
+    p.n_scales = scale ? (N / 2) / cols_per_scale : 0;
     p.t_tiles = (T + TILE - 1) / TILE;
     p.t_group = t_group < 1 || t_group > p.t_tiles ? p.t_tiles : t_group;
     const long long all_a = (N + bn_a - 1) / bn_a;
@@ -489,4 +503,11 @@ IB_EXPORT int ib_gemm_pair(const void* x, int ldx, const void* w, int ldw, void*
     if (rc != IB_OK) return rc;
     return swiglu ? launch_pair<true>(mx, mw, mw2, p, pairs, (cudaStream_t)stream)
                   : launch_pair<false>(mx, mw, mw2, p, pairs, (cudaStream_t)stream);
+}
+
+IB_EXPORT int ib_gemm_pair(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int T, int N,
+                           int K, int swiglu, int bn_a, int cols_a, int bn_b, int t_group, int sm_count,
+                           unsigned* err, void* stream) {
+    return ib_gemm_pair_scaled(x, ldx, w, ldw, out, ldo, T, N, K, swiglu, bn_a, cols_a, bn_b, t_group, sm_count,
+                               nullptr, 0, err, stream);
 }

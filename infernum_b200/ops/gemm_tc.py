@@ -20,6 +20,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from ..csrc.build import load_module
+from ..errors import KernelError
 from . import core
 
 _c_int, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_void_p, ctypes.c_longlong
@@ -79,6 +80,10 @@ def pair_lib() -> ctypes.CDLL:
                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                                    _c_void_p]
         l.ib_gemm_pair.restype = _c_int
+        l.ib_gemm_pair_scaled.argtypes = [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int,
+                                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                                          _c_int, _c_void_p, _c_void_p]
+        l.ib_gemm_pair_scaled.restype = _c_int
         lib()  # the SM count
         _pair_lib = l
     return _pair_lib
@@ -187,19 +192,31 @@ def choose_token_group(T: int, K: int) -> int:
 
 def gemm_pair(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor,
               err: Optional[torch.Tensor] = None, swiglu: bool = False,
-              tiling: Optional[Tuple[int, int, int]] = None, token_group: Optional[int] = None) -> None:
+              tiling: Optional[Tuple[int, int, int]] = None, token_group: Optional[int] = None,
+              scale: Optional[torch.Tensor] = None, cols_per_scale: int = 0) -> None:
     """The product for many tokens: tiles of 256 tokens x up to 256 weight rows,
     each computed by two SMs as one (tcgen05 ``cta_group::2``); bf16 out.
-    ``swiglu`` as in ``gemm_tc``, for any number of tokens."""
+    ``swiglu`` as in ``gemm_tc``, for any number of tokens.  ``scale`` (with
+    ``swiglu``; float32 [T, I / cols_per_scale], contiguous): every output is also
+    multiplied by ``scale[t, column // cols_per_scale]``, as the outputs of experts
+    side by side are by the weights a token's router gave them."""
     core.require_cuda(x, w, out)
     T, K = x.shape
     N = w.shape[0]
+    if scale is not None:
+        if not swiglu or cols_per_scale <= 0 or cols_per_scale % 16 or (N // 2) % cols_per_scale:
+            raise KernelError("gemm_pair: a scale goes with the gated epilogue and runs of a multiple of 16 columns")
+        if scale.dtype != torch.float32 or not scale.is_contiguous() \
+                or tuple(scale.shape) != (T, (N // 2) // cols_per_scale):
+            raise KernelError(f"gemm_pair: scale must be contiguous float32 [{T}, {(N // 2) // cols_per_scale}]")
+        core.require_cuda(scale)
     bn_a, cols_a, bn_b = tiling or choose_pair_tiling(T, N, POLICY["sm_count"], swiglu)
-    code = pair_lib().ib_gemm_pair(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
-                                   out.stride(0), T, N, K, int(swiglu), bn_a, cols_a, bn_b,
-                                   token_group or choose_token_group(T, K), POLICY["sm_count"],
-                                   (err if err is not None else _error_word(x.device)).data_ptr(),
-                                   core.stream_ptr(x))
+    code = pair_lib().ib_gemm_pair_scaled(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(),
+                                          out.stride(0), T, N, K, int(swiglu), bn_a, cols_a, bn_b,
+                                          token_group or choose_token_group(T, K), POLICY["sm_count"],
+                                          scale.data_ptr() if scale is not None else None, int(cols_per_scale),
+                                          (err if err is not None else _error_word(x.device)).data_ptr(),
+                                          core.stream_ptr(x))
     core.check(code, "gemm_pair")
 
 
@@ -225,11 +242,13 @@ def route(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, err: Optional[tor
 
 
 def swiglu_route(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor,
-                 err: Optional[torch.Tensor] = None, activation: str = "silu") -> bool:
+                 err: Optional[torch.Tensor] = None, activation: str = "silu",
+                 scale: Optional[torch.Tensor] = None, cols_per_scale: int = 0) -> bool:
     """The gate/up product with SiLU(gate) * up applied in its epilogue, when
     the policy and the operands allow; ``out`` is [T, I].  Up to 64 tokens go to
     the kernel that streams the weights once (decode), prompts to the kernel on
-    pairs of SMs when their length suits its tiles (``pair_suits``)."""
+    pairs of SMs when their length suits its tiles (``pair_suits``).  With
+    ``scale`` (see ``gemm_pair``) only the latter is offered."""
     mode = POLICY["mode"]
     if mode in ("none", "cublas", "library") or activation not in GATE_CODES:
         return False
@@ -239,11 +258,15 @@ def swiglu_route(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor
     if not eligible(x, w_interleaved, out) or out.stride(0) % 8 or out.data_ptr() % 16:
         return False
     T = x.shape[0]
+    if scale is not None and (cols_per_scale <= 0 or cols_per_scale % 16):
+        return False
     if T <= min(POLICY["max_tokens"], 64):
+        if scale is not None:
+            return False
         gemm_tc(x, w_interleaved, out, splits=1, swiglu=code, err=err)
         return True
     if pair_suits(T, fused_activation=True):
-        gemm_pair(x, w_interleaved, out, swiglu=code, err=err)
+        gemm_pair(x, w_interleaved, out, swiglu=code, err=err, scale=scale, cols_per_scale=cols_per_scale)
         return True
     return False
 

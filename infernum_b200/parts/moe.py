@@ -136,6 +136,14 @@ class MixtureOfExperts(FeedForward):
     def forward(self, x: torch.Tensor, ctx=None) -> torch.Tensor:
         _ids, _wts, gate = self.route(x)
         act = torch.empty((x.shape[0], self.experts * self.expert_size), dtype=x.dtype, device=x.device)
-        core.gated_act(self.gate_up(x), act, self.activation, block=self.block, scale=gate,
-                       cols_per_scale=self.expert_size)
+        fused = False
+        if self.block == 64 and x.dtype == torch.bfloat16 and self.gate_up.weight.dtype == torch.bfloat16:
+            from ..ops import gemm_tc
+
+            # prompts: activation and the router's weights in the product's epilogue
+            fused = gemm_tc.swiglu_route(x, self.gate_up.weight, act, self.gate_up.err, activation=self.activation,
+                                         scale=gate, cols_per_scale=self.expert_size)
+        if not fused:
+            core.gated_act(self.gate_up(x), act, self.activation, block=self.block, scale=gate,
+                           cols_per_scale=self.expert_size)
         return self.down(act)

@@ -562,6 +562,39 @@ def test_gemm_pair_with_swiglu_epilogue(T, I, K, tiling):
     assert rel_err(out, want) < 6e-3
 
 
+@pytest.mark.parametrize("T, experts, ff, K, act", [(256, 4, 64, 64, "silu"), (300, 3, 48, 200, "gelu_tanh"),
+                                                    (700, 8, 128, 512, "silu"), (513, 4, 16, 72, "silu")])
+def test_gemm_pair_gated_epilogue_with_a_scale_per_run_of_columns(T, experts, ff, K, act):
+    """Experts side by side: every output is also multiplied by the weight its token gave the
+    expert it belongs to; zeros (experts not chosen) give exact zeros."""
+    from infernum_b200.ops import gemm_tc
+    I = experts * ff
+    if I % 64:
+        pytest.skip("the gate and up rows are interleaved 64 by 64")
+    g = torch.Generator().manual_seed(I + T)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16)
+    wu = (torch.randn(I, K, generator=g) * 0.2).to(torch.bfloat16)
+    w = torch.stack([wg.view(I // 64, 64, K), wu.view(I // 64, 64, K)], dim=1).reshape(2 * I, K)
+    scale = torch.rand(T, experts, generator=g) * 2.0
+    scale[torch.rand(T, experts, generator=g) < 0.4] = 0.0
+    out = torch.full((T, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    gemm_tc.gemm_pair(x.to(DEV), w.contiguous().to(DEV), out, swiglu=gemm_tc.GATE_CODES[act],
+                      scale=scale.to(DEV), cols_per_scale=ff)
+    assert gemm_tc.error_flags(DEV) == 0
+    gate, up = x.double() @ wg.double().T, x.double() @ wu.double().T
+    if act == "silu":
+        a = gate / (1 + torch.exp(-gate))
+    else:
+        a = 0.5 * gate * (1 + torch.tanh(0.7978845608028654 * (gate + 0.044715 * gate ** 3)))
+    want = a * up * scale.double().repeat_interleave(ff, dim=1)
+    assert rel_err(out, want) < 6e-3
+    zero = scale.repeat_interleave(ff, dim=1) == 0
+    assert bool((out.cpu()[zero] == 0).all())
+    with pytest.raises(Exception):
+        gemm_tc.gemm_pair(x.to(DEV), w.contiguous().to(DEV), out, swiglu=1, scale=scale.to(DEV), cols_per_scale=ff + 8)
+
+
 def test_gemm_pair_refuses_widths_it_cannot_run():
     from infernum_b200.errors import KernelError
     from infernum_b200.ops import gemm_tc
