@@ -87,8 +87,21 @@ CASE_D = {
     "architecture": "Bolovik", "vocab": 97, "width": 64, "norm": {"eps": 1e-5, "groups": 4},
     "layers": [delta(2, 1, 32, 24, 3, None), attention(4, 2, 16, 12, 0.3, 9, 2, rot(8, 1000.0), None)],
 }
-CASES = {"A": CASE_A, "B": CASE_B, "C": CASE_C, "D": CASE_D}
-PAGE_SIZES = {"A": 4, "B": 8, "C": 16, "D": 4}
+# Models of one kind of mixer only: delta layers alone use no pages, attention layers alone no
+# state slots; attention as the first layer; all experts chosen, without groups.
+CASE_E = {
+    "architecture": "Bolovik", "vocab": 101, "width": 48, "norm": {"eps": 1e-5, "groups": 2},
+    "layers": [delta(2, 2, 16, 16, 2, DENSE(40)), delta(4, 1, 8, 8, 4, moe(16, 4, 2, (2, 2))),
+               delta(3, 3, 16, 8, 3, None)],
+}
+CASE_F = {
+    "architecture": "Bolovik", "vocab": 89, "width": 64, "norm": {"eps": 1e-5, "groups": 1},
+    "layers": [attention(4, 2, 16, 16, 0.25, 12, 2, rot(16, 1000.0), DENSE(64)),
+               attention(2, 2, 32, 32, 0.2, None, None, rot(16, 10000.0, (4.0, 1.0, 4.0, 32)), None),
+               attention(4, 1, 16, 16, 0.3, 5, None, None, moe(24, 4, 4))],
+}
+CASES = {"A": CASE_A, "B": CASE_B, "C": CASE_C, "D": CASE_D, "E": CASE_E, "F": CASE_F}
+PAGE_SIZES = {"A": 4, "B": 8, "C": 16, "D": 4, "E": 8, "F": 16}
 
 
 def make_folder(folder: str, config: dict, seed: int, sharpen: float = 0.0, drop: Optional[list] = None,

@@ -22,8 +22,8 @@ pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
 DTYPES = ["float32", "bfloat16"]
 LENGTHS = {"A": [31, 45, 1, 2, 90, 17], "B": [23, 60, 3, 1, 41, 8], "C": [130, 75, 2, 200, 33, 64],
-           "D": [50, 3, 27, 1, 12]}
-NAMES = ["A", "B", "C", "D", "Asharp", "Csharp"]
+           "D": [50, 3, 27, 1, 12], "E": [40, 2, 19, 66, 1], "F": [70, 33, 2, 1, 48]}
+NAMES = ["A", "B", "C", "D", "E", "F", "Asharp", "Csharp"]
 
 
 @pytest.fixture(scope="module")
@@ -60,7 +60,7 @@ def replay(models, name, dtype, steps, tmp_path, max_tokens=None):
 
 def names_for(dtype):
     # (where attention is peaked, bfloat16 rounding of a score is multiplied on its way to the logits)
-    return NAMES if dtype == "float32" else ["A", "B", "C", "D"]
+    return NAMES if dtype == "float32" else ["A", "B", "C", "D", "E", "F"]
 
 
 # In bfloat16 a router logit carries the rounding of everything before it; where the last chosen
@@ -282,7 +282,7 @@ def check_greedy(plain, prompt, got, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "Csharp"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F", "Csharp"])
 def test_greedy_generation_through_the_engine(models, name, dtype):
     import infernum_b200 as ib
     if name not in names_for(dtype):
