@@ -523,7 +523,7 @@ __global__ void delta_prepare_kernel(const T* __restrict__ x, int x_stride, int 
         }
         sq = warp_sum(sq);
         sk = warp_sum(sk);
-        const float iq = rsqrtf((float)dk) / sqrtf(sq + 1e-6f), ik = 1.f / sqrtf(sk + 1e-6f);
+        const float iq = (float)(1.0 / sqrt((double)dk)) / sqrtf(sq + 1e-6f), ik = 1.f / sqrtf(sk + 1e-6f);
         float2* dst = kq + ((size_t)g * n_rows + row) * dk;
         for (int i = lane; i < dk; i += 32) {
             const float kn = k[i] * ik, qn = q[i] * iq;
