@@ -77,7 +77,7 @@ CASE_C = {
     "layers": [
         attention(8, 2, 32, 32, 0.2, 45, None, rot(16, 10000.0), DENSE(192)),
         delta(4, 2, 64, 32, 4, moe(64, 8, 2, (4, 2))),
-        attention(4, 4, 64, 64, 0.15, 40, 17, rot(64, 500000.0, (4.0, 1.0, 4.0, 128)), None),
+        attention(4, 4, 64, 64, 0.15, 40, 17, rot(64, 250000.0, (3.0, 1.0, 5.0, 128)), None),
         delta(2, 1, 128, 16, 3, DENSE(96)),
         attention(4, 1, 64, 64, 0.15, None, None, rot(32, 10000.0), moe(32, 4, 2)),
     ],
