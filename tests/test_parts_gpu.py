@@ -250,18 +250,18 @@ def test_products_report_into_the_runtimes_error_word(monkeypatch):
     rt = runtime(torch.bfloat16)
     seen = {"few": [], "pair": []}
     few, pair = gemm_tc.lib(), gemm_tc.pair_lib()
-    real_few, real_pair = few.ib_gemm_tc, pair.ib_gemm_pair
+    real_few, real_pair = few.ib_gemm_tc, pair.ib_gemm_pair_scaled
 
     def spy_few(*args):
         seen["few"].append(args[12])
         return real_few(*args)
 
     def spy_pair(*args):
-        seen["pair"].append(args[15])
+        seen["pair"].append(args[17])
         return real_pair(*args)
 
     monkeypatch.setattr(few, "ib_gemm_tc", spy_few)
-    monkeypatch.setattr(pair, "ib_gemm_pair", spy_pair)
+    monkeypatch.setattr(pair, "ib_gemm_pair_scaled", spy_pair)
     lin = Linear(torch.randn(160, 96, device=DEV).to(torch.bfloat16), rt)
     lin(torch.randn(5, 96, device=DEV).to(torch.bfloat16))          # few tokens
     lin(torch.randn(768, 96, device=DEV).to(torch.bfloat16))        # a prompt: pairs of SMs
