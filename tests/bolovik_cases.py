@@ -100,6 +100,53 @@ CASE_F = {
                attention(2, 2, 32, 32, 0.2, None, None, rot(16, 10000.0, (4.0, 1.0, 4.0, 32)), None),
                attention(4, 1, 16, 16, 0.3, 5, None, None, moe(24, 4, 4))],
 }
+
+
+def random_case(seed: int) -> dict:
+    """A configuration drawn at random from sizes a small model might have: widths, part counts,
+    layer orders, head counts and sizes (values narrower or wider than keys), taps, windows with
+    and without kept tokens, rotation over none, part or all of a head with and without rescaled
+    frequencies, experts with and without groups, layers without a feed-forward."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([128, 192, 256, 320, 384])
+    parts = rng.choice([g for g in (1, 2, 4, 8) if width % g == 0])
+    layers = []
+    for _ in range(rng.randint(3, 6)):
+        r = rng.random()
+        if r < 0.2:
+            mlp = None
+        elif r < 0.55:
+            mlp = DENSE(rng.choice([128, 200, 256]))
+        else:
+            experts = rng.choice([4, 6, 8, 12, 16])
+            count = rng.choice([g for g in (1, 2, 3, 4) if experts % g == 0])
+            keep = rng.randint(1, count)
+            if rng.random() < 0.8:
+                mlp = moe(rng.choice([32, 64, 96]), experts, rng.randint(1, min(keep * (experts // count), 6)),
+                          (count, keep))
+            else:
+                mlp = moe(rng.choice([32, 64, 96]), experts, rng.randint(1, min(experts, 6)))
+        if rng.random() < 0.5:
+            heads = rng.choice([2, 4, 6, 8])
+            kv = rng.choice([h for h in (1, 2, 3, 4, 8) if heads % h == 0])
+            dim = rng.choice([32, 48, 64, 96, 128])
+            layers.append(delta(heads, kv, dim, rng.choice([32, 64, 128, dim]), rng.choice([2, 3, 4, 5]), mlp))
+        else:
+            heads = rng.choice([2, 4, 8, 16])
+            kv = rng.choice([h for h in (1, 2, 4, 8) if heads % h == 0])
+            dim = rng.choice([32, 64, 96, 128])
+            window = rng.choice([None, 32, 48, 64, 100, 128])
+            keep_first = rng.choice([None, 0, 1, 4, 16, 20, 33]) if window else None
+            rd = rng.choice([0, dim // 4, dim // 2, dim])
+            scaling = rng.choice([None, (4.0, 1.0, 4.0, 512), (8.0, 1.0, 4.0, 256), (2.0, 2.0, 8.0, 64)])
+            layers.append(attention(heads, kv, dim, rng.choice([dim, dim, 32, 64]), rng.choice([dim ** -0.5, 0.1, 0.2]),
+                                    window, keep_first, rot(rd, rng.choice([100.0, 10000.0, 250000.0]), scaling) if rd else None,
+                                    mlp))
+    return {"architecture": "Bolovik", "vocab": rng.choice([300, 512, 777, 1000]), "width": width,
+            "norm": {"eps": rng.choice([1e-5, 1e-6]), "groups": parts}, "layers": layers}
+
+
 CASES = {"A": CASE_A, "B": CASE_B, "C": CASE_C, "D": CASE_D, "E": CASE_E, "F": CASE_F}
 PAGE_SIZES = {"A": 4, "B": 8, "C": 16, "D": 4, "E": 8, "F": 16}
 

@@ -14,7 +14,7 @@ import pytest
 import torch
 
 import plain_bolovik as pb
-from bolovik_cases import CASES, PAGE_SIZES, make_folder
+from bolovik_cases import CASES, PAGE_SIZES, make_folder, random_case
 from helpers import (ROOT, TOL, compare_trace, peak_tokens, random_tokens, run_trace_inprocess,
                      run_trace_subprocess, trace_mixed, trace_portions, trace_tail, trace_whole)
 
@@ -192,6 +192,27 @@ def test_long_decoding(models, name, dtype, tmp_path):
     steps = trace_tail("long", seqs["long"], tail=226)
     out, plain = replay(models, name, dtype, steps, tmp_path)
     compare(steps, out, seqs, plain, dtype, name)
+
+
+@pytest.mark.parametrize("seed", [2, 3, 5, 8, 13, 21])
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Sizes, orders and constants nobody chose by hand: mixed batches with pages and slots used again,
+    then a long tail decoded token by token, in 32-bit against the plain implementation."""
+    cfg = random_case(seed)
+    folder = make_folder(str(tmp_path / "m"), cfg, seed=seed, gain=0.0)
+    plain = pb.Plain(folder)
+    seqs = {f"r{i}": random_tokens(n, cfg["vocab"], 31 * i + n) for i, n in enumerate([150, 70, 2, 19 + seed, 129, 1])}
+    for rid, seq in seqs.items():
+        # a router whose two candidates lie within 32-bit rounding of each other (scores that
+        # saturate) may choose either: the sequence ends before such a token
+        close = (plain.margins(seq) < 1e-4).nonzero().flatten().tolist()
+        if close:
+            seqs[rid] = seq[:max(close[0], 1)]
+    steps = trace_mixed(seqs, max_live=4, seed=seed)
+    if len(seqs["r0"]) > 3:
+        steps += trace_tail("r0", seqs["r0"], 140, step0=len(steps))
+    out = run_trace_inprocess(folder, "float32", steps, str(tmp_path / "out"), max(peak_tokens(steps), 256), 16)
+    compare_trace(steps, out, seqs, plain, TOL["float32"] * F32_SLACK)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
