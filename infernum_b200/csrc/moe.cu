@@ -7,10 +7,10 @@
 // One warp per row; the row is kept in shared memory and a chosen logit is
 // struck out there.
 //
-// A second way of scoring (ib_moe_route_scored): scores s = sigmoid(z); the experts
-// form `n_groups` equal groups of neighbours, a group's score is the sum of its
-// `group_top` largest scores, and only experts of the `keep` best groups can be
-// chosen (n_groups <= 1: all can); the `top` largest scores among those are
+// A second way of scoring (ib_moe_route_scored): s_e = sigmoid(z_e); expert e belongs to
+// group floor(e / (E / n_groups)); G_g = the sum of the `group_top` largest s_e of group g;
+// the `keep` groups with the largest G_g stay open and the others' experts are struck out
+// (n_groups <= 1: nothing is struck out); the `top` largest scores among those are
 // chosen, the lower index among equals, and are the weights as they are - or,
 // with `renorm`, divided by their sum.
 #include "common.cuh"

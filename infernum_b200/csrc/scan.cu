@@ -8,7 +8,7 @@
 //         S[i][j] <- w_t[i] S[i][j] + k_t[i] v_t[j]
 //   ssd:  S[n][p] <- a_t S[n][p] + B_t[n] (dt_t x_t[p]),   y_t[p] = sum_n C_t[n] S[n][p] + D x_t[p]
 //   delta: S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
-//         (a gated delta rule: the read-out sees the token's own write)
+//         (a gated delta rule; o_t is taken from the state after its update)
 //
 // Everything a token brings - (r, k, w, u k) per key channel and v for wkv; (B, C)
 // per state row, x, and (dt, a) per head for ssd - has been made in 32-bit by a

@@ -33,7 +33,7 @@ to the softmax's denominator; it has no key and no value and is not scaled);
 ``biases`` ({"q": name, "k": name, "v": name}: biases of the three projections);
 ``unit_norm`` ({"eps": e, "value": bool}: after the rotation, queries and keys are
 divided by their root mean square per head, without a weight; with ``value`` each
-value head likewise, and it is cached so); may be combined with a rotary ``position``;
+value head likewise before it is written to the pages); may be combined with a rotary ``position``;
 ``keep_first`` (with a window: the first so many tokens of a request stay visible
 to every later query, at their own positions).
 """

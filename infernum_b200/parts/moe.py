@@ -22,9 +22,9 @@ down), ``router`` and ``router_bias`` (names behind the prefix; bias None for
 none); ``scoring``: "softmax_top" (default, as above) or "sigmoid": the scores
 are ``sigmoid(z)``, the ``top`` largest are chosen and are the weights as they
 are (``renormalize``: divided by their sum); with ``groups`` ({"count", "keep",
-"top": 2}) the experts form ``count`` equal groups of neighbours, a group's
-score is the sum of its ``top`` largest scores and only experts of the best
-``keep`` groups can be chosen.
+"top": 2}) expert e belongs to group ``e // (experts // count)``, a group is
+scored by the sum of the ``top`` largest scores in it, and the experts outside
+the ``keep`` best-scored groups are struck out before the choice.
 """
 
 from __future__ import annotations

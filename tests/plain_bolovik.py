@@ -191,8 +191,8 @@ def dense_ff(h, W, p: str):
 
 def route(h, router_w, r: dict):
     """Per token: (chosen expert ids, their weights).  Scores are sigmoids of the
-    router's logits; experts form equal groups of neighbours, a group's score is
-    the sum of its two largest scores, only the best ``keep`` groups stay open; of
+    router's logits; expert e is in group e // (E // count); a group is scored by
+    its two largest scores added up, and only the ``keep`` best-scored groups stay open; of
     those the ``top`` largest scores are chosen and are the weights as they are."""
     E, top = int(r["experts"]), int(r["top"])
     s = torch.sigmoid(h @ router_w.t())  # [T, E]
