@@ -44,6 +44,7 @@ class LayerCache:
     page_size: int = 0
     num_pages: int = 0
     state: Optional[torch.Tensor] = None  # [slots, *shape]
+    block_state: Optional[torch.Tensor] = None  # [slots, *shape]: state of the layer's arrangement itself
     owner: bool = True  # False: this run reads another run's cache and must not write
 
 
@@ -82,8 +83,9 @@ class CacheManager:
     def __init__(self, needs: Sequence, page_size: int, num_pages, max_requests: int,
                  dtype: torch.dtype = torch.bfloat16, device=None, memory_fraction: float = 0.9):
         """``needs``: one item per schedule position with attributes
-        ``paged`` (PagedCacheSpec or None), ``state`` (StateSpec or None) and
-        ``cache_of`` (an earlier position or None).  ``num_pages`` sizes the
+        ``paged`` (PagedCacheSpec or None), ``state`` (StateSpec or None),
+        ``cache_of`` (an earlier position or None) and, optionally,
+        ``block_state`` (StateSpec or None: state of the layer's arrangement).  ``num_pages`` sizes the
         groups' pools: one number for all of them, a sequence with one number
         per group (groups are numbered in the order in which the schedule first
         needs them), or a function of the group's ``PagedCacheSpec`` - a group
@@ -154,6 +156,12 @@ class CacheManager:
                     lc.state = torch.zeros((self.max_requests + 1, *need.state.shape),
                                            dtype=need.state.dtype, device=device)
                     self._state_tensors.append(lc.state)
+            block_state = getattr(need, "block_state", None)
+            if block_state is not None and device is not None:
+                # (every run has its own, also one that reads another run's pages)
+                lc.block_state = torch.zeros((self.max_requests + 1, *block_state.shape), dtype=block_state.dtype,
+                                             device=device)
+                self._state_tensors.append(lc.block_state)
             self.layer_caches.append(lc)
 
         if not isinstance(self._pages_arg, int) and not callable(self._pages_arg) \

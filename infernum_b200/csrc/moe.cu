@@ -224,3 +224,137 @@ IB_EXPORT int ib_moe_route_scored(const float* logits, int ld, const float* bias
     IB_LAUNCH_CHECK();
     return IB_OK;
 }
+
+// A third way of scoring (ib_moe_route_softmax_all): s = softmax(z) over all E_all router
+// outputs; the choice is made by s_e + correction_e (the lower index among equals), the
+// weights are the chosen s_e (without the correction) over their sum + 1e-20.  The last
+// E_all - E outputs have no expert behind them: choosing one hands the token's input on
+// with that weight.  Written: ids / weights [N, top]; the dense row gate[N, E] for the
+// experts that exist; extra[N, 2] = (the sum of the weights that fell on the outputs
+// without an expert, sigmoid(z[E_all]) when the logits carry one more column - the gate of
+// an expert that every token uses - else 1).
+__global__ void moe_route_softmax_all_kernel(const float* __restrict__ logits, int ld,
+                                             const float* __restrict__ correction, int E_all, int E, int top,
+                                             int with_gate, int* __restrict__ ids, float* __restrict__ weights,
+                                             float* __restrict__ gate, float* __restrict__ extra) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float sm[];
+    float* s = sm;          // [E_all] the scores
+    float* c = sm + E_all;  // [E_all] the choice values, struck out as they are chosen
+    const int row = blockIdx.x, lane = threadIdx.x;
+    const float* src = logits + (size_t)row * ld;
+    float zmax = -INFINITY;
+    for (int e = lane; e < E_all; e += 32) zmax = fmaxf(zmax, src[e]);
+    zmax = warp_max(zmax);
+    float part = 0.f;
+    for (int e = lane; e < E_all; e += 32) {
+        const float p = expf(src[e] - zmax);
+        s[e] = p;
+        part += p;
+    }
+    const float denom = warp_sum(part);
+    __syncwarp();
+    for (int e = lane; e < E_all; e += 32) {
+        const float v = s[e] / denom;
+        s[e] = v;
+        c[e] = v + (correction ? correction[e] : 0.f);
+        if (gate && e < E) gate[(size_t)row * E + e] = 0.f;
+    }
+    __syncwarp();
+    float sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = E_all;
+        for (int e = lane; e < E_all; e += 32) {
+            const float v = c[e];
+            if (v > best || (v == best && e < at)) { best = v; at = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at >= E_all) at = k < E_all ? k : 0;  // a row of NaN: any output
+        sum += s[at];
+        if (lane == 0) {
+            ids[(size_t)row * top + k] = at;
+            c[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const float inv = 1.f / (sum + 1e-20f);
+        float passed = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int at = ids[(size_t)row * top + k];
+            const float w = s[at] * inv;
+            weights[(size_t)row * top + k] = w;
+            if (at < E) {
+                if (gate) gate[(size_t)row * E + at] = w;
+            } else {
+                passed += w;
+            }
+        }
+        if (extra) {
+            extra[(size_t)row * 2] = passed;
+            extra[(size_t)row * 2 + 1] = with_gate ? 1.f / (1.f + expf(-src[E_all])) : 1.f;
+        }
+    }
+}
+
+IB_EXPORT int ib_moe_route_softmax_all(const float* logits, int ld, const float* correction, int E_all, int E, int top,
+                                       int with_gate, int* ids, float* weights, float* gate, float* extra,
+                                       int n_rows, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!logits || !ids || !weights || E_all <= 0 || E < 0 || E > E_all || top <= 0 || top > E_all ||
+        ld < E_all + (with_gate ? 1 : 0))
+        return IB_ERR_BAD_ARG;
+    const size_t smem = (size_t)E_all * 2 * sizeof(float);
+    if (smem > 48 * 1024) return IB_ERR_TOO_LARGE;
+    cudaError_t le = launch_kernel(moe_route_softmax_all_kernel, dim3(n_rows), dim3(32), smem, (cudaStream_t)stream,
+                                   logits, ld, correction, E_all, E, top, with_gate, ids, weights, gate, extra);
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// out[n, :] = routed[n, :] + extra[n, 0] * h[n, :] + extra[n, 1] * shared[n, :]: the experts' weighted
+// sum, the input handed on by the outputs without an expert, and the expert that every token uses behind
+// its gate; `routed` and `shared` may be absent.  32-bit arithmetic, one rounding at the store.
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ routed, const T* __restrict__ h, int h_stride,
+                                   const T* __restrict__ shared, const float* __restrict__ extra,
+                                   T* __restrict__ out, int n_rows, int W) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    const float passed = extra[(size_t)row * 2], g = extra[(size_t)row * 2 + 1];
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < W; i += gridDim.y * blockDim.x) {
+        float v = routed ? to_f32(routed[(size_t)row * W + i]) : 0.f;
+        v = fmaf(passed, to_f32(h[(size_t)row * h_stride + i]), v);
+        if (shared) v = fmaf(g, to_f32(shared[(size_t)row * W + i]), v);
+        out[(size_t)row * W + i] = from_f32<T>(v);
+    }
+}
+
+IB_EXPORT int ib_moe_combine(const void* routed, const void* h, int h_stride, const void* shared, const float* extra,
+                             void* out, int dtype, int n_rows, int W, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!h || !extra || !out || W <= 0 || h_stride < W) return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_rows, (W + 1023) / 1024), block(W >= 1024 ? 256 : 128);
+    cudaError_t le;
+    if (dtype == 0)
+        le = launch_kernel(moe_combine_kernel<float>, grid, block, 0, s, (const float*)routed, (const float*)h, h_stride,
+                           (const float*)shared, extra, (float*)out, n_rows, W);
+    else if (dtype == 1)
+        le = launch_kernel(moe_combine_kernel<bf16>, grid, block, 0, s, (const bf16*)routed, (const bf16*)h, h_stride,
+                           (const bf16*)shared, extra, (bf16*)out, n_rows, W);
+    else
+        return IB_ERR_UNSUPPORTED;
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}

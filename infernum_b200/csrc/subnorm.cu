@@ -254,3 +254,119 @@ IB_EXPORT int ib_part_rmsnorm(const float* x, const int* row_idx, const float* w
     IB_LAUNCH_CHECK();
     return IB_OK;
 }
+
+// Layers that norm both what a sub-layer reads and what it returns, with a gate on the
+// result and a fixed factor on the addition:
+//   X = x + mult * n(y * sigmoid(g + b))
+// y: the sub-layer's result, g: the gate's projection (both of the activation dtype, g may
+// lie in wider rows), b: the gate's bias (float32, may be null; g null: no gate).  One CTA
+// per (row, part); the gated values are formed twice (sum of squares, then the store)
+// rather than kept, 32-bit throughout.
+template <typename T>
+__global__ void gated_norm_add_kernel(const float* __restrict__ x_in, const T* __restrict__ y,
+                                      const T* __restrict__ g, int g_stride, const float* __restrict__ gb,
+                                      const float* __restrict__ w, float eps, float mult,
+                                      float* __restrict__ out_res, T* __restrict__ out_act, int W, int part) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int row = blockIdx.x, c0 = blockIdx.y * part;
+    const size_t base = (size_t)row * W + c0;
+    const T* yp = y + base;
+    const T* gp = g ? g + (size_t)row * g_stride + c0 : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+        float v = to_f32(yp[i]);
+        if (gp) v = v / (1.f + expf(-(to_f32(gp[i]) + (gb ? gb[c0 + i] : 0.f))));
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)part + eps);
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+        float v = to_f32(yp[i]);
+        if (gp) v = v / (1.f + expf(-(to_f32(gp[i]) + (gb ? gb[c0 + i] : 0.f))));
+        const float X = fmaf(mult, v * inv * w[c0 + i], x_in[base + i]);
+        out_res[base + i] = X;
+        if (out_act) out_act[base + i] = from_f32<T>(X);
+    }
+}
+
+IB_EXPORT int ib_gated_norm_add(const float* x_in, const void* y, const void* g, int g_stride, const float* gb,
+                                int act_dtype, const float* w, float eps, float mult, float* out_res, void* out_act,
+                                int n_rows, int W, int parts, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!x_in || !y || !w || !out_res || W <= 0 || parts <= 0 || W % parts || !(eps > 0.f) || (g && g_stride < W))
+        return IB_ERR_BAD_ARG;
+    if (parts > 65535) return IB_ERR_TOO_LARGE;
+    const int part = W / parts;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_rows, parts), block(part_threads(part));
+    cudaError_t le;
+    if (act_dtype == 0)
+        le = launch_kernel(gated_norm_add_kernel<float>, grid, block, 0, s, x_in, (const float*)y, (const float*)g,
+                           g_stride, gb, w, eps, mult, out_res, (float*)out_act, W, part);
+    else if (act_dtype == 1)
+        le = launch_kernel(gated_norm_add_kernel<bf16>, grid, block, 0, s, x_in, (const bf16*)y, (const bf16*)g,
+                           g_stride, gb, w, eps, mult, out_res, (bf16*)out_act, W, part);
+    else
+        return IB_ERR_UNSUPPORTED;
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// The part norm of 32-bit rows written back in 32-bit (an embedding that is normed before
+// it becomes the stream).
+IB_EXPORT int ib_part_rmsnorm_f32(const float* x, const float* w, float eps, float* out, int n_rows, int W, int parts,
+                                  void* stream) {
+    return ib_part_rmsnorm(x, nullptr, w, eps, out, 0, n_rows, W, parts, stream);
+}
+
+// Two 32-bit streams side by side in the activation dtype: out[n] = [a[n] | b[n]], the
+// input of a product that reads both.
+template <typename T>
+__global__ void concat_round_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out,
+                                    int W) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < 2 * W; i += gridDim.y * blockDim.x)
+        out[(size_t)row * 2 * W + i] = from_f32<T>(i < W ? a[(size_t)row * W + i] : b[(size_t)row * W + i - W]);
+}
+
+IB_EXPORT int ib_concat_round(const float* a, const float* b, void* out, int act_dtype, int n_rows, int W,
+                              void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!a || !b || !out || W <= 0) return IB_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(n_rows, (2 * W + 1023) / 1024), block(128);
+    cudaError_t le;
+    if (act_dtype == 0)
+        le = launch_kernel(concat_round_kernel<float>, grid, block, 0, s, a, b, (float*)out, W);
+    else if (act_dtype == 1)
+        le = launch_kernel(concat_round_kernel<bf16>, grid, block, 0, s, a, b, (bf16*)out, W);
+    else
+        return IB_ERR_UNSUPPORTED;
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// x[n, :] += v[:] on 32-bit rows, in place (a learned vector added to every token's stream).
+__global__ void add_row_kernel(float* __restrict__ x, const float* __restrict__ v, int W) {
+    pdl_trigger();
+    pdl_wait();
+    const int row = blockIdx.x;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < W; i += gridDim.y * blockDim.x)
+        x[(size_t)row * W + i] += v[i];
+}
+
+IB_EXPORT int ib_add_row(float* x, const float* v, int n_rows, int W, void* stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (!x || !v || W <= 0) return IB_ERR_BAD_ARG;
+    cudaError_t le = launch_kernel(add_row_kernel, dim3(n_rows, (W + 1023) / 1024), dim3(128), 0, (cudaStream_t)stream,
+                                   x, v, W);
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}

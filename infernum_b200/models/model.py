@@ -14,7 +14,7 @@ import torch
 
 from ..errors import ConfigError
 from ..ops import core
-from ..parts import (EMBEDDINGS, HEADS, NORMS, Block, ModelSpec, PagedCacheSpec, ResidualStream,
+from ..parts import (EMBEDDINGS, ENTRIES, HEADS, NORMS, Block, ModelSpec, PagedCacheSpec, ResidualStream,
                      Runtime, StateSpec, WeightSpec, build_layer)
 
 
@@ -26,6 +26,7 @@ class CacheNeed:
     paged: Optional[PagedCacheSpec]
     state: Optional[StateSpec]
     cache_of: Optional[int]  # reads the cache of this earlier schedule position
+    block_state: Optional[StateSpec] = None  # state of the layer's arrangement itself, per run
 
 
 class Model:
@@ -37,7 +38,10 @@ class Model:
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, rt)
         self.head = HEADS.get(spec.lm_head.kind)(spec.lm_head.params, rt)
         self.schedule = tuple(spec.schedule)
+        self.pass_entry = ENTRIES.get(spec.pass_entry.kind)(spec.pass_entry.params, rt) if spec.pass_entry else None
         for pos, item in enumerate(self.schedule):
+            if item.enter is not None and self.pass_entry is None:
+                raise ConfigError(f"schedule[{pos}] begins a pass, the model names no pass entry")
             if not 0 <= item.layer < len(self.layers):
                 raise ConfigError(f"schedule[{pos}] names layer {item.layer}, there are "
                                   f"{len(self.layers)}")
@@ -49,7 +53,8 @@ class Model:
 
     # ---- declarations -------------------------------------------------------
     def _all_parts(self):
-        return [self.embedding, *self.layers, self.final_norm, self.head]
+        extra = [self.pass_entry] if self.pass_entry is not None else []
+        return [self.embedding, *extra, *self.layers, self.final_norm, self.head]
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         specs: Dict[str, WeightSpec] = {}
@@ -78,7 +83,7 @@ class Model:
             mixer = self.layers[item.layer].mixer
             paged = mixer.cache_spec() if mixer is not None else None
             state = mixer.state_spec() if mixer is not None else None
-            needs.append(CacheNeed(pos, paged, state, item.cache_of))
+            needs.append(CacheNeed(pos, paged, state, item.cache_of, self.layers[item.layer].state_spec()))
         embed_state = self.embedding.state_spec() if hasattr(self.embedding, "state_spec") else None
         if embed_state is not None:
             needs.append(CacheNeed(len(self.schedule), None, embed_state, None))
@@ -90,6 +95,8 @@ class Model:
         total = self.final_norm.weight_bytes() + self.head.weight_bytes()
         for item in self.schedule:
             total += self.layers[item.layer].weight_bytes()
+            if item.enter is not None:
+                total += self.pass_entry.weight_bytes()
         return total
 
     # ---- the forward pass of one step ---------------------------------------
@@ -108,6 +115,8 @@ class Model:
             else:
                 stream = ResidualStream(self.embedding.forward(ctx.token_ids))
             for item, cache in zip(self.schedule, caches):
+                if item.enter is not None:
+                    self.pass_entry.forward(stream, item.enter)
                 self.layers[item.layer].forward(stream, ctx, cache)
             if ctx.logit_rows is None or ctx.logit_rows.numel() == 0:
                 return None

@@ -17,7 +17,8 @@ from ..csrc.build import load_module
 from ..errors import KernelError
 
 CORE_SOURCES = ["elementwise.cu", "attention_plain.cu", "gemm_plain.cu", "sampling.cu", "layernorm.cu",
-                "embed_hashed.cu", "latent.cu", "moe.cu", "hyper.cu", "recurrent.cu", "subnorm.cu"]
+                "embed_hashed.cu", "latent.cu", "moe.cu", "hyper.cu", "recurrent.cu", "subnorm.cu", "shortconv.cu",
+                "attention_diff.cu"]
 
 _c_int = ctypes.c_int
 _c_float = ctypes.c_float
@@ -152,6 +153,31 @@ def core_lib() -> ctypes.CDLL:
             getattr(lib, fn).restype = _c_int
         for fn in ("ib_attention_plain_ex", "ib_gemm_plain_batched", "ib_gated_act", "ib_scale_add_norm",
                    "ib_softcap", "ib_embed_hashed", "ib_latent_prepare", "ib_latent_q_rotate", "ib_moe_route"):
+            getattr(lib, fn).restype = _c_int
+        lib.ib_latent_prepare_ex.argtypes = lib.ib_latent_prepare.argtypes[:22] + [_c_int, _c_float, _c_void_p, _c_void_p]
+        lib.ib_latent_q_rotate_ex.argtypes = lib.ib_latent_q_rotate.argtypes[:14] + [_c_int, _c_float, _c_void_p]
+        lib.ib_moe_route_softmax_all.argtypes = [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                                                 _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p]
+        lib.ib_moe_combine.argtypes = [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                                       _c_int, _c_void_p]
+        lib.ib_gated_norm_add.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_float,
+                                          _c_float, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p]
+        lib.ib_concat_round.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p]
+        lib.ib_add_row.argtypes = [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p]
+        lib.ib_causal_conv.argtypes = [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_ll, _c_void_p, _c_void_p,
+                                       _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p]
+        lib.ib_conv_state_update.argtypes = [_c_void_p, _c_int, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_int,
+                                             _c_int, _c_int, _c_void_p]
+        lib.ib_conv_rope_append.argtypes = [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p,
+                                            _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
+                                            _c_float, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                            _c_int, _c_int, _c_int, _c_void_p, _c_void_p]
+        lib.ib_attention_diff.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                          _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                          _c_float, _c_float, _c_float, _c_float, _c_float, _c_void_p, _c_void_p]
+        for fn in ("ib_latent_prepare_ex", "ib_latent_q_rotate_ex", "ib_moe_route_softmax_all", "ib_moe_combine",
+                   "ib_gated_norm_add", "ib_concat_round", "ib_add_row", "ib_causal_conv", "ib_conv_state_update",
+                   "ib_conv_rope_append", "ib_attention_diff"):
             getattr(lib, fn).restype = _c_int
         for fn in ("ib_decode_advance", "ib_feed_tokens", "ib_embed", "ib_add_rmsnorm", "ib_residual_add", "ib_rope_append",
                    "ib_silu_mul", "ib_attention_plain", "ib_gemm_plain", "ib_argmax", "ib_sample"):
@@ -685,12 +711,15 @@ def latent_prepare(lat: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, r
                    wq: Optional[torch.Tensor], wkv: Optional[torch.Tensor], eps: float,
                    inv_freq: Optional[torch.Tensor], positions: torch.Tensor, row_entry: torch.Tensor,
                    block_tables: Optional[torch.Tensor], cq_out: Optional[torch.Tensor],
-                   pool: Optional[torch.Tensor], err: torch.Tensor) -> None:
+                   pool: Optional[torch.Tensor], err: torch.Tensor, adjacent: bool = False,
+                   magnitude: float = 1.0) -> None:
     """From the down projections ``lat`` [N, q_rank + kv_rank + rot_dim] (float32 or
     the activation dtype; the norms and the rotation are 32-bit either way):
     the normed query latent into ``cq_out``, and - with ``pool`` - the normed
     key/value latent and the rotated shared key part into the token's place in
-    the pool [pages, 1, page_size, kv_rank + rot_dim]."""
+    the pool [pages, 1, page_size, kv_rank + rot_dim].  ``adjacent``: the rotation
+    pairs neighbours (2i, 2i + 1) instead of (i, i + rotary_dim / 2); ``magnitude``
+    multiplies cosine and sine."""
     require_cuda(lat, wq, wkv, inv_freq, positions, row_entry, block_tables, cq_out, pool, err)
     _int32(positions, "positions")
     _int32(row_entry, "row_entry")
@@ -713,17 +742,18 @@ def latent_prepare(lat: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, r
         max_blocks = block_tables.shape[1]
         if rotary_dim and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rotary_dim // 2):
             raise KernelError("latent_prepare: inv_freq must be float32 [rotary_dim / 2]")
-    check(core_lib().ib_latent_prepare(lat.data_ptr(), dtype_code(lat.dtype), lat.stride(0), int(q_rank), int(kv_rank), int(rot_dim),
+    check(core_lib().ib_latent_prepare_ex(lat.data_ptr(), dtype_code(lat.dtype), lat.stride(0), int(q_rank), int(kv_rank), int(rot_dim),
                                        int(rotary_dim), _ptr(wq), _ptr(wkv), float(eps), _ptr(inv_freq),
                                        positions.data_ptr(), row_entry.data_ptr(), _ptr(block_tables), max_blocks,
                                        _ptr(cq_out), _ptr(pool), dtype_code(act), page_size, num_pages,
-                                       1 if write_kv else 0, lat.shape[0], err.data_ptr(), stream_ptr(lat)),
+                                       1 if write_kv else 0, lat.shape[0], 1 if adjacent else 0, float(magnitude),
+                                       err.data_ptr(), stream_ptr(lat)),
           "latent_prepare")
 
 
 def latent_q_rotate(q: torch.Tensor, heads: int, dim: int, rot_dim: int, rotary_dim: int,
                     inv_freq: Optional[torch.Tensor], positions: torch.Tensor, q_abs: torch.Tensor,
-                    offset: int) -> None:
+                    offset: int, adjacent: bool = False, magnitude: float = 1.0) -> None:
     """The rotated part of each head of ``q`` [N, heads * (dim + rot_dim)], rotated
     by its row's position, into ``q_abs[N, heads, offset : offset + rot_dim]``."""
     require_cuda(q, inv_freq, positions, q_abs)
@@ -731,10 +761,11 @@ def latent_q_rotate(q: torch.Tensor, heads: int, dim: int, rot_dim: int, rotary_
     if q.dim() != 2 or q.stride(1) != 1 or q_abs.dim() != 3 or q_abs.stride(2) != 1 or q_abs.dtype != q.dtype \
             or q_abs.shape[0] != q.shape[0] or q_abs.shape[1] != heads or q_abs.shape[2] < offset + rot_dim:
         raise KernelError("latent_q_rotate: q [N, heads*(dim+rot)] and q_abs [N, heads, >= offset+rot] do not fit")
-    check(core_lib().ib_latent_q_rotate(q.data_ptr(), q.stride(0), int(heads), int(dim), int(rot_dim),
+    check(core_lib().ib_latent_q_rotate_ex(q.data_ptr(), q.stride(0), int(heads), int(dim), int(rot_dim),
                                         int(rotary_dim), _ptr(inv_freq), positions.data_ptr(), q_abs.data_ptr(),
                                         q_abs.stride(0), q_abs.stride(1), int(offset), dtype_code(q.dtype),
-                                        q.shape[0], stream_ptr(q)), "latent_q_rotate")
+                                        q.shape[0], 1 if adjacent else 0, float(magnitude), stream_ptr(q)),
+          "latent_q_rotate")
 
 
 def attention_latent_plain(q_abs: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, kv_rank: int,
@@ -1109,3 +1140,198 @@ def moe_route_scored(logits: torch.Tensor, bias: Optional[torch.Tensor], top: in
     check(core_lib().ib_moe_route_scored(logits.data_ptr(), logits.stride(0), _ptr(bias), E, int(top), int(groups),
                                          int(keep), int(group_top), 1 if renorm else 0, ids.data_ptr(),
                                          weights.data_ptr(), _ptr(gate), N, stream_ptr(logits)), "moe_route_scored")
+
+
+# ---------------------------------------------------------------------------
+# Layers that norm what a sub-layer reads and what it returns, with a short
+# convolution on the input and a gate on the result; a stream that re-enters a
+# run of layers together with the embedding's output; attention with two score
+# maps per head; routing by a softmax over all router outputs, some of which
+# hand the input on.
+# ---------------------------------------------------------------------------
+def gated_norm_add(x_in: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor], gate_bias: Optional[torch.Tensor],
+                   weight: torch.Tensor, parts: int, eps: float, mult: float, out_res: torch.Tensor,
+                   out_act: Optional[torch.Tensor] = None) -> None:
+    """``out_res = x_in + mult * n(y * sigmoid(gate + gate_bias))`` with ``n`` the RMS norm
+    over ``parts`` equal consecutive parts of a row times ``weight`` (float32).
+    ``gate`` None: the result is normed as it is; it may be a view of wider rows.
+    ``x_in`` and ``out_res`` (float32) may be one buffer."""
+    require_cuda(x_in, y, gate, gate_bias, weight, out_res, out_act)
+    N, W = x_in.shape
+    for t, name in ((x_in, "x_in"), (out_res, "out_res")):
+        if t.dtype != torch.float32 or t.shape != (N, W) or not t.is_contiguous():
+            raise KernelError(f"gated_norm_add: {name} must be contiguous float32 [{N}, {W}]")
+    if y.shape != (N, W) or not y.is_contiguous() or (out_act is not None and (
+            out_act.shape != (N, W) or out_act.dtype != y.dtype or not out_act.is_contiguous())):
+        raise KernelError("gated_norm_add: y and out_act must be contiguous [N, W] of one dtype")
+    if gate is not None and (gate.shape != (N, W) or gate.stride(1) != 1 or gate.dtype != y.dtype):
+        raise KernelError("gated_norm_add: the gate must be [N, W] of y's dtype with unit inner stride")
+    _f32_vec(weight, W, "gated_norm_add: weight")
+    _f32_vec(gate_bias, W, "gated_norm_add: gate bias")
+    if parts <= 0 or W % parts:
+        raise KernelError(f"gated_norm_add: a row of {W} does not split in {parts} parts")
+    check(core_lib().ib_gated_norm_add(x_in.data_ptr(), y.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                       _ptr(gate_bias), dtype_code(y.dtype), weight.data_ptr(), float(eps), float(mult),
+                                       out_res.data_ptr(), _ptr(out_act), N, W, int(parts), stream_ptr(y)),
+          "gated_norm_add")
+
+
+def concat_round(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n] = [a[n] | b[n]] rounded to ``out``'s dtype; ``a``, ``b`` float32 [N, W]."""
+    require_cuda(a, b, out)
+    N, W = a.shape
+    if a.dtype != torch.float32 or b.dtype != torch.float32 or b.shape != (N, W) or not a.is_contiguous() \
+            or not b.is_contiguous() or out.shape != (N, 2 * W) or not out.is_contiguous():
+        raise KernelError("concat_round: a, b contiguous float32 [N, W], out contiguous [N, 2 W]")
+    check(core_lib().ib_concat_round(a.data_ptr(), b.data_ptr(), out.data_ptr(), dtype_code(out.dtype), N, W,
+                                     stream_ptr(a)), "concat_round")
+
+
+def add_row(x: torch.Tensor, v: torch.Tensor) -> None:
+    """x[n, :] += v in place; ``x`` float32 [N, W], ``v`` float32 [W]."""
+    require_cuda(x, v)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous():
+        raise KernelError("add_row: x must be contiguous float32 [N, W]")
+    _f32_vec(v, x.shape[1], "add_row: v")
+    check(core_lib().ib_add_row(x.data_ptr(), v.data_ptr(), x.shape[0], x.shape[1], stream_ptr(x)), "add_row")
+
+
+def causal_conv(x: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor], state_offset: int, ctx,
+                out: torch.Tensor, add_input: bool = False) -> None:
+    """Per channel ``out_t = (x_t if add_input) + sum_j weight[:, j] x_(t - taps + 1 + j)`` over each
+    entry's rows in order; the ``taps - 1`` inputs before an entry's first row come from the request's
+    state (``state[slot, offset : offset + (taps - 1) C]``, float32, oldest first).  ``x`` [N, C] may be
+    a view of wider rows; ``weight`` float32 [C, taps].  The state is not changed: ``conv_state_update``
+    does that once every row has read it."""
+    require_cuda(x, weight, state, out)
+    N, C = x.shape
+    taps = weight.shape[1]
+    if x.stride(1) != 1 or out.shape != (N, C) or out.stride(1) != 1 or out.dtype != x.dtype:
+        raise KernelError("causal_conv: x and out must be [N, C] of one dtype with unit inner stride")
+    if weight.dtype != torch.float32 or weight.shape != (C, taps) or not weight.is_contiguous():
+        raise KernelError("causal_conv: the filters must be contiguous float32 [C, taps]")
+    ptr, stride = _state_view(state, state_offset) if taps > 1 else (None, 0)
+    check(core_lib().ib_causal_conv(x.data_ptr(), x.stride(0), dtype_code(x.dtype), weight.data_ptr(), ptr, stride,
+                                    ctx.row_entry.data_ptr(), ctx.cu_rows.data_ptr(), ctx.slot_ids.data_ptr(),
+                                    out.data_ptr(), out.stride(0), N, C, taps, 1 if add_input else 0, stream_ptr(x)),
+          "causal_conv")
+
+
+def conv_state_update(x: torch.Tensor, taps: int, state: torch.Tensor, state_offset: int, ctx) -> None:
+    """The convolution's state after the step: the last ``taps - 1`` rows of (old state, then the entry's
+    rows of ``x``), per entry; an entry without rows keeps its state."""
+    if taps <= 1:
+        return
+    require_cuda(x, state)
+    N, C = x.shape
+    if x.stride(1) != 1:
+        raise KernelError("conv_state_update: x must have unit inner stride")
+    ptr, stride = _state_view(state, state_offset)
+    check(core_lib().ib_conv_state_update(x.data_ptr(), x.stride(0), dtype_code(x.dtype), ptr, stride,
+                                          ctx.cu_rows.data_ptr(), ctx.slot_ids.data_ptr(), ctx.n_entries, C, int(taps),
+                                          stream_ptr(x)), "conv_state_update")
+
+
+def conv_rope_append(x: torch.Tensor, weight: Optional[torch.Tensor], state: Optional[torch.Tensor], state_offset: int,
+                     inv_freq: Optional[torch.Tensor], rotary_dim: int, magnitude: float, n_heads: int, n_kv_heads: int,
+                     dim: int, vdim: int, ctx, block_tables: torch.Tensor, q_out: torch.Tensor, k_pool: torch.Tensor,
+                     v_pool: torch.Tensor, err: torch.Tensor) -> None:
+    """Rows of ``x``: ``n_heads`` query heads of two maps of ``dim``, ``n_kv_heads`` key heads of two maps,
+    ``n_kv_heads`` values of ``vdim``, as projected.  Each channel goes through its short causal
+    convolution (``weight`` float32 [C, taps]; None: none), every map of a query or key is rotated in its
+    first ``rotary_dim`` dimensions (neighbours paired); queries go to ``q_out`` [N, n_heads * 2 dim], keys
+    and values to their pages ([pages, n_kv_heads, page_size, 2 dim] and [.., vdim])."""
+    require_cuda(x, weight, state, inv_freq, block_tables, q_out, k_pool, v_pool, err)
+    _int32(block_tables, "block_tables")
+    N = x.shape[0]
+    C = (n_heads + n_kv_heads) * 2 * dim + n_kv_heads * vdim
+    taps = 0 if weight is None else weight.shape[1]
+    if x.dim() != 2 or x.stride(1) != 1 or x.shape[1] < C:
+        raise KernelError("conv_rope_append: x rows must hold queries, keys and values with unit inner stride")
+    if weight is not None and (weight.dtype != torch.float32 or weight.shape != (C, taps) or not weight.is_contiguous()):
+        raise KernelError("conv_rope_append: the filters must be contiguous float32 [C, taps]")
+    num_pages, nkv_pool, page_size, kw = k_pool.shape
+    if nkv_pool != n_kv_heads or kw != 2 * dim or v_pool.shape != (num_pages, n_kv_heads, page_size, vdim) \
+            or k_pool.dtype != x.dtype or v_pool.dtype != x.dtype or not k_pool.is_contiguous() \
+            or not v_pool.is_contiguous():
+        raise KernelError("conv_rope_append: pools must be contiguous [pages, kv_heads, page_size, 2 dim | vdim] of x's dtype")
+    if q_out.shape != (N, n_heads * 2 * dim) or q_out.dtype != x.dtype or not q_out.is_contiguous():
+        raise KernelError("conv_rope_append: q_out must be contiguous [N, heads * 2 dim] of x's dtype")
+    if rotary_dim:
+        _f32_vec(inv_freq, rotary_dim // 2, "conv_rope_append: inv_freq")
+        if inv_freq is None:
+            raise KernelError("conv_rope_append: a rotation needs its frequencies")
+    ptr, stride = _state_view(state, state_offset) if taps > 1 else (None, 0)
+    check(core_lib().ib_conv_rope_append(x.data_ptr(), x.stride(0), dtype_code(x.dtype), _ptr(weight), taps, ptr, stride,
+                                         ctx.positions.data_ptr(), ctx.row_entry.data_ptr(), ctx.cu_rows.data_ptr(),
+                                         ctx.slot_ids.data_ptr(), block_tables.data_ptr(), block_tables.shape[1],
+                                         _ptr(inv_freq), int(rotary_dim), float(magnitude), n_heads, n_kv_heads, dim,
+                                         vdim, q_out.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), page_size,
+                                         num_pages, N, err.data_ptr(), stream_ptr(x)), "conv_rope_append")
+
+
+def attention_diff(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, ctx,
+                   block_tables: torch.Tensor, n_heads: int, scale: float, softcap: float, lam: float, eps: float,
+                   out_scale: float, err: torch.Tensor) -> None:
+    """Two causal softmax maps per head over shared values, ``o = A_1 V - lam A_2 V``, each head's ``o``
+    divided by its root mean square (``eps`` inside the root) and multiplied by ``out_scale``.  ``q``
+    [N, n_heads * 2 dim] holds a head's two queries side by side, the key pool a key head's two keys
+    ([pages, kv_heads, page_size, 2 dim]); scores are ``softcap * tanh(q . k * scale / softcap)``
+    (``softcap`` 0: uncapped).  ``out`` [N, n_heads * vdim].  32-bit arithmetic."""
+    require_cuda(q, k_pool, v_pool, out, block_tables, err)
+    _int32(block_tables, "block_tables")
+    N = q.shape[0]
+    num_pages, nkv, page_size, kw = k_pool.shape
+    vdim = v_pool.shape[3]
+    if kw % 2 or q.shape != (N, n_heads * kw) or not q.is_contiguous() or out.shape != (N, n_heads * vdim) \
+            or not out.is_contiguous() or q.dtype != k_pool.dtype or out.dtype != q.dtype or v_pool.dtype != q.dtype \
+            or v_pool.shape[:3] != k_pool.shape[:3] or not k_pool.is_contiguous() or not v_pool.is_contiguous():
+        raise KernelError("attention_diff: q [N, heads * 2 dim], out [N, heads * vdim] and the pools do not fit")
+    check(core_lib().ib_attention_diff(q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
+                                       dtype_code(q.dtype), ctx.positions.data_ptr(), ctx.row_entry.data_ptr(),
+                                       block_tables.data_ptr(), block_tables.shape[1], N, n_heads, nkv, kw // 2, vdim,
+                                       page_size, num_pages, float(scale), float(softcap or 0.0), float(lam), float(eps),
+                                       float(out_scale), err.data_ptr(), stream_ptr(q)), "attention_diff")
+
+
+def moe_route_softmax_all(logits: torch.Tensor, correction: Optional[torch.Tensor], outputs: int, experts: int, top: int,
+                          ids: torch.Tensor, weights: torch.Tensor, gate: Optional[torch.Tensor],
+                          extra: Optional[torch.Tensor]) -> None:
+    """Routing by ``s = softmax(logits[:, :outputs])``: the ``top`` largest ``s + correction`` are chosen
+    (lowest index among equals), their weights are ``s`` over the chosen ones' sum (+ 1e-20).  Outputs
+    from ``experts`` on have no expert: their weight is summed into ``extra[:, 0]``.  ``gate`` [N, experts]
+    gets the dense weights of the experts that exist.  When ``logits`` has one more column, ``extra[:, 1]``
+    is its sigmoid, else 1."""
+    require_cuda(logits, correction, ids, weights, gate, extra)
+    _int32(ids, "ids")
+    N, cols = logits.shape
+    if cols not in (outputs, outputs + 1) or logits.dtype != torch.float32 or logits.stride(1) != 1 \
+            or ids.shape != (N, top) or not ids.is_contiguous() or weights.shape != (N, top) \
+            or weights.dtype != torch.float32 or not weights.is_contiguous():
+        raise KernelError("moe_route_softmax_all: logits float32 [N, outputs (+ 1)], ids int32 and weights float32 [N, top]")
+    _f32_vec(correction, outputs, "moe_route_softmax_all: correction")
+    if gate is not None and (gate.dtype != torch.float32 or gate.shape != (N, experts) or not gate.is_contiguous()):
+        raise KernelError("moe_route_softmax_all: gate must be contiguous float32 [N, experts]")
+    if extra is not None and (extra.dtype != torch.float32 or extra.shape != (N, 2) or not extra.is_contiguous()):
+        raise KernelError("moe_route_softmax_all: extra must be contiguous float32 [N, 2]")
+    check(core_lib().ib_moe_route_softmax_all(logits.data_ptr(), logits.stride(0), _ptr(correction), int(outputs),
+                                              int(experts), int(top), 1 if cols == outputs + 1 else 0, ids.data_ptr(),
+                                              weights.data_ptr(), _ptr(gate), _ptr(extra), N, stream_ptr(logits)),
+          "moe_route_softmax_all")
+
+
+def moe_combine(routed: Optional[torch.Tensor], h: torch.Tensor, shared: Optional[torch.Tensor], extra: torch.Tensor,
+                out: torch.Tensor) -> None:
+    """out = routed + extra[:, 0] * h + extra[:, 1] * shared, row by row ([N, W]; ``h`` may be a view of
+    wider rows; ``routed`` and ``shared`` may be None)."""
+    require_cuda(routed, h, shared, extra, out)
+    N, W = out.shape
+    if h.shape != (N, W) or h.stride(1) != 1 or h.dtype != out.dtype or not out.is_contiguous():
+        raise KernelError("moe_combine: h and out must be [N, W] of one dtype")
+    for t in (routed, shared):
+        if t is not None and (t.shape != (N, W) or t.dtype != out.dtype or not t.is_contiguous()):
+            raise KernelError("moe_combine: routed and shared must be contiguous [N, W] of out's dtype")
+    if extra.dtype != torch.float32 or extra.shape != (N, 2) or not extra.is_contiguous():
+        raise KernelError("moe_combine: extra must be contiguous float32 [N, 2]")
+    check(core_lib().ib_moe_combine(_ptr(routed), h.data_ptr(), h.stride(0), _ptr(shared), extra.data_ptr(), out.data_ptr(),
+                                    dtype_code(out.dtype), N, W, stream_ptr(out)), "moe_combine")

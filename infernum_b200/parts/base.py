@@ -86,10 +86,14 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleItem:
     """One run of a layer.  ``cache_of`` names an earlier schedule position
-    whose cache this run reads instead of owning one."""
+    whose cache this run reads instead of owning one.  ``enter``: this run is
+    the first of pass number ``enter`` through a run of layers that the model
+    walks several times; the model's ``pass_entry`` part transforms the stream
+    before it."""
 
     layer: int
     cache_of: Optional[int] = None
+    enter: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -106,6 +110,8 @@ class ModelSpec:
     bos_token_id: Optional[int] = None
     # checkpoint tensors that may be present without being used
     ignorable: Tuple[str, ...] = ()
+    # what happens to the stream where a schedule item has ``enter`` (an ENTRIES kind)
+    pass_entry: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -272,6 +278,12 @@ class Block(Part):
         m = self.parts.get("mixer")
         return m if isinstance(m, Mixer) else None
 
+    def state_spec(self) -> Optional[StateSpec]:
+        """Per-request state of the arrangement itself, beside its mixer's (the
+        inputs a convolution on what the sub-layers read still needs, say); one
+        flat float32 vector per slot and scheduled run, in ``cache.block_state``."""
+        return None
+
     def weight_specs(self) -> Dict[str, WeightSpec]:
         specs: Dict[str, WeightSpec] = {}
         for part in self.parts.values():
@@ -315,6 +327,9 @@ class ResidualStream:
         # results: float32 [slots, N, hidden], slot 0 the embedding's output, slot
         # j the result of layer j - 1; filled as the layers run.
         self.results: Optional[torch.Tensor] = None
+        # The embedding's output (float32 [N, hidden]) for models whose layers meet
+        # it again; never written over.
+        self.origin: Optional[torch.Tensor] = None
 
     def push(self, delta: torch.Tensor, write=None) -> None:
         if self.pending is not None:
@@ -376,6 +391,7 @@ POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("output head")
+ENTRIES = Registry("pass entry")
 
 _ROLE_REGISTRY = {
     "mixer": MIXERS,

@@ -20,6 +20,11 @@ does write, read and norm in one pass over the row.
 then ``x <- x + norm2(ffn(x))``; the sub-layers read the stream itself.  With
 ``depth_average`` the layer's result is kept and what goes on is a weighted sum
 of the embedding's output and all layers' results so far.
+
+``sandwich``: norms on both sides of a sub-layer and a fixed factor on the sum:
+``x <- x + mult * norm1b(g1 * mixer(c1(norm1(x))))``, then the same with ``ffn``;
+``c`` adds a short causal convolution of the normed rows to them, ``g`` is a
+sigmoid gate computed from the normed rows.
 """
 
 from __future__ import annotations
@@ -27,7 +32,9 @@ from __future__ import annotations
 from ..errors import ConfigError
 import torch
 
-from .base import BLOCKS, Block, ResidualStream, WeightSpec
+from ..ops import core
+from .base import BLOCKS, Block, ResidualStream, StateSpec, WeightSpec
+from .linear import Linear
 
 
 @BLOCKS.register("prenorm")
@@ -186,3 +193,87 @@ class SubNormBlock(Block):
         p["norm1"].add_normed(stream, y, depth if ffn is None else None)
         if ffn is not None:
             p["norm2"].add_normed(stream, ffn.forward(stream.act, ctx), depth)
+
+
+@BLOCKS.register("sandwich")
+class SandwichBlock(Block):
+    """For sub-layer n in (1: ``mixer``, 2: ``ffn``), with ``h = norm<n>(x)``:
+
+        u = h + conv_n(h)                     (``canon``: a causal convolution per channel over time,
+                                               ``taps`` wide, no bias; zeros before the sequence)
+        y = f_n(u) * sigmoid(W_gn h + b_gn)   (``gates``; the gate reads h, not u)
+        x <- x + mult * norm<n>b(y)
+
+    The sum stays 32-bit.  The last ``taps - 1`` normed rows of either sub-layer
+    are the arrangement's state of a request ([2, taps - 1, hidden] floats per
+    slot and scheduled run).  The norms after the sub-layers must offer
+    ``add_gated`` (``part_rmsnorm`` does).
+
+    Parameters: ``hidden_size``, ``mult`` (default 1), ``canon`` (None or {"taps",
+    "names": (n1, n2)}), ``gates`` (None or {"names": (n1, n2)}: tensors ``<name>``
+    [hidden, hidden] and ``<name>.b``).  Parts: ``norm1``, ``norm1b``, ``mixer`` and,
+    optionally, ``norm2``, ``norm2b``, ``ffn``.
+    """
+
+    def __init__(self, params, rt, parts):
+        super().__init__(params, rt, parts)
+        self.hidden_size = int(params["hidden_size"])
+        self.mult = float(params.get("mult", 1.0))
+        need = ["norm1", "norm1b", "mixer"] + (["norm2", "norm2b"] if "ffn" in parts else [])
+        missing = [r for r in need if r not in parts]
+        if missing:
+            raise ConfigError(f"sandwich block {params.get('name', '')!r} lacks parts {missing}")
+        for role in ("norm1b", "norm2b"):
+            if role in parts and not hasattr(parts[role], "add_gated"):
+                raise ConfigError(f"sandwich block: the {parts[role].kind!r} norm cannot norm a gated result")
+        canon = params.get("canon") or {}
+        self.taps = int(canon.get("taps") or 0)
+        self.canon_names = tuple(canon.get("names") or ()) if self.taps else ()
+        gates = params.get("gates") or {}
+        self.gate_names = tuple(gates.get("names") or ())
+        self.subs = [(0, "norm1", "mixer", "norm1b")] + ([(1, "norm2", "ffn", "norm2b")] if "ffn" in parts else [])
+        self.canon_w = {}
+        self.gate = {}
+
+    def state_spec(self):
+        if self.taps <= 1:
+            return None
+        return StateSpec((2 * (self.taps - 1) * self.hidden_size,), torch.float32)
+
+    def weight_specs(self):
+        specs = super().weight_specs()
+        h = self.hidden_size
+        for n, _, _, _ in self.subs:
+            if self.taps:
+                specs[self.canon_names[n]] = WeightSpec((h, self.taps), init="normal", std=0.3)
+            if self.gate_names:
+                specs[self.gate_names[n]] = WeightSpec((h, h))
+                specs[self.gate_names[n] + ".b"] = WeightSpec((h,), init="normal", std=0.5)
+        return specs
+
+    def bind(self, weights) -> None:
+        super().bind(weights)
+        for n, _, _, _ in self.subs:
+            if self.taps:
+                self.canon_w[n] = weights[self.canon_names[n]].to(torch.float32).contiguous()
+            if self.gate_names:
+                self.gate[n] = (Linear(weights[self.gate_names[n]], self.rt),
+                                weights[self.gate_names[n] + ".b"].to(torch.float32).contiguous())
+
+    def weight_bytes(self) -> int:
+        return super().weight_bytes() + sum(lin.nbytes for lin, _ in self.gate.values())
+
+    def forward(self, stream: ResidualStream, ctx, cache) -> None:
+        p = self.parts
+        for n, pre, role, post in self.subs:
+            h = p[pre].forward(stream)
+            gate = self.gate.get(n)
+            g = gate[0](h) if gate is not None else None
+            u = h
+            if self.taps:
+                state, off = cache.block_state, n * (self.taps - 1) * self.hidden_size
+                u = torch.empty_like(h)
+                core.causal_conv(h, self.canon_w[n], state, off, ctx, u, add_input=True)
+                core.conv_state_update(h, self.taps, state, off, ctx)
+            y = p[role].forward(u, ctx, cache) if role == "mixer" else p[role].forward(u, ctx)
+            p[post].add_gated(stream, y, g, gate[1] if gate is not None else None, self.mult)

@@ -17,6 +17,7 @@ from typing import Dict, Optional
 
 import torch
 
+from ..errors import ConfigError
 from ..ops import core
 from .base import EMBEDDINGS, HEADS, Embedding, Part, ResidualStream, Runtime, StateSpec, WeightSpec
 from .linear import Linear
@@ -28,7 +29,10 @@ class TokenEmbedding(Embedding):
     stream also carries its rounding to the activation dtype, for layers whose
     sub-layers read the stream itself); ``result_slots`` (n > 0: the stream keeps
     room for n results - the embedding's output, in slot 0, and every layer's -
-    for layers that hand on a weighted sum of them)."""
+    for layers that hand on a weighted sum of them); ``norm`` (a norm spec {"kind",
+    "params"} with ``apply_f32``: the looked-up rows are normed, in 32-bit, before
+    they become the stream); ``keep_origin`` (True: the stream keeps the embedding's
+    output, as this part leaves it, in ``stream.origin``)."""
 
     def __init__(self, params, rt: Runtime):
         super().__init__(params, rt)
@@ -37,9 +41,27 @@ class TokenEmbedding(Embedding):
         self.weight_name = params["weight"]
         self.with_act = bool(params.get("act", False))
         self.result_slots = int(params.get("result_slots") or 0)
+        self.keep_origin = bool(params.get("keep_origin", False))
+        self.norm = None
+        if params.get("norm"):
+            from .base import NORMS
+
+            self.norm = NORMS.get(params["norm"]["kind"])(params["norm"].get("params", {}), rt)
+            if not hasattr(self.norm, "apply_f32"):
+                raise ConfigError(f"token embedding: the {self.norm.kind!r} norm has no 32-bit form")
+            if self.with_act or self.result_slots:
+                raise ConfigError("token embedding: a normed embedding keeps no activation copy or results")
         self.weight: Optional[torch.Tensor] = None
 
     def forward_step(self, ctx, cache) -> ResidualStream:
+        if self.norm is not None or self.keep_origin:
+            x = self.forward(ctx.token_ids)
+            if self.norm is not None:
+                x = self.norm.apply_f32(x)
+            stream = ResidualStream(x)
+            if self.keep_origin:
+                stream.origin = x
+            return stream
         if not self.with_act and not self.result_slots:
             return ResidualStream(self.forward(ctx.token_ids))
         n, dev = ctx.token_ids.numel(), ctx.token_ids.device
@@ -58,10 +80,15 @@ class TokenEmbedding(Embedding):
         return stream
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {self.weight_name: WeightSpec((self.vocab_size, self.hidden_size))}
+        specs = {self.weight_name: WeightSpec((self.vocab_size, self.hidden_size))}
+        if self.norm is not None:
+            specs.update(self.norm.weight_specs())
+        return specs
 
     def bind(self, weights) -> None:
         self.weight = weights[self.weight_name].contiguous()
+        if self.norm is not None:
+            self.norm.bind(weights)
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         out = torch.empty((token_ids.numel(), self.hidden_size), dtype=torch.float32,

@@ -30,6 +30,12 @@ window: pages are given back by it.
 Norms, angles, scores and softmax are 32-bit.  Rotation pairs element i with
 i + rotary_dim / 2 of the rotated part; ``rotary_dim`` <= ``rot_dim``.
 
+Without a query latent (``q_rank`` 0 or None) the queries are a projection of
+``h`` itself, ``q = W_q h`` (tensor ``q``), made in one product with ``W_dkv h``.
+``rotary_pairing: "adjacent"`` rotates neighbours (2i, 2i + 1) instead;
+``rotary_scaling`` rescales the frequencies (``rope.rotary_inv_freq``) and, for
+"ramp" scaling, multiplies cosine and sine by its magnitude.
+
 Parameters: ``hidden_size``, ``num_heads``, ``dim``, ``rot_dim``, ``vdim``,
 ``q_rank``, ``kv_rank``, ``scale``, ``window`` (0 = all keys), ``cache_window``
 (default: window), ``eps``, ``rotary_dim`` (default rot_dim), ``theta``,
@@ -48,9 +54,9 @@ from ..ops import core
 from ..ops import attention as attn_ops
 from .base import MIXERS, Mixer, PagedCacheSpec, Runtime, WeightSpec
 from .linear import Linear, batched_matmul_nt
-from .rope import rotary_inv_freq
+from .rope import rotary_inv_freq, rotary_magnitude
 
-_DEFAULT_NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm",
+_DEFAULT_NAMES = {"q": "q", "dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm",
                   "uk": "uk", "uv": "uv", "o": "o"}
 
 
@@ -61,7 +67,7 @@ class LatentAttention(Mixer):
         g = lambda k: int(params[k])  # noqa: E731
         self.hidden_size, self.num_heads = g("hidden_size"), g("num_heads")
         self.dim, self.rot_dim, self.vdim = g("dim"), g("rot_dim"), g("vdim")
-        self.q_rank, self.kv_rank = g("q_rank"), g("kv_rank")
+        self.q_rank, self.kv_rank = int(params.get("q_rank") or 0), g("kv_rank")
         self.scale = float(params["scale"])
         self.window = int(params.get("window") or 0)
         self.cache_window = int(params.get("cache_window", self.window) or 0)
@@ -76,7 +82,10 @@ class LatentAttention(Mixer):
         self.prefix = params.get("prefix", "")
         names = {**_DEFAULT_NAMES, **(params.get("names") or {})}
         self.names = {k: self.prefix + v for k, v in names.items()}
-        freqs = rotary_inv_freq(self.rotary_dim, float(params.get("theta", 10000.0)), None) if self.rotary_dim else []
+        scaling = params.get("rotary_scaling")
+        self.adjacent = params.get("rotary_pairing", "half") == "adjacent"
+        self.magnitude = rotary_magnitude(scaling)
+        freqs = rotary_inv_freq(self.rotary_dim, float(params.get("theta", 10000.0)), scaling) if self.rotary_dim else []
         self.inv_freq = torch.tensor(freqs, dtype=torch.float64).to(torch.float32).to(rt.device) \
             if freqs else None
         self.width = self.kv_rank + self.rot_dim  # of a cached vector and of a query in latent space
@@ -90,14 +99,16 @@ class LatentAttention(Mixer):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         H, n = self.num_heads, self.names
-        specs = {
+        specs = {n["q"]: WeightSpec((H * (self.dim + self.rot_dim), self.hidden_size))} if not self.q_rank else {
             n["dq"]: WeightSpec((self.q_rank, self.hidden_size)),
             n["dq_norm"]: WeightSpec((self.q_rank,), init="norm"),
             n["uq"]: WeightSpec((H * (self.dim + self.rot_dim), self.q_rank)),
+        }
+        specs.update({
             n["uk"]: WeightSpec((H * self.dim, self.kv_rank)),
             n["uv"]: WeightSpec((H * self.vdim, self.kv_rank)),
             n["o"]: WeightSpec((self.hidden_size, H * self.vdim)),
-        }
+        })
         if not self.kv_shared:
             specs[n["dkv"]] = WeightSpec((self.kv_rank + self.rot_dim, self.hidden_size))
             specs[n["dkv_norm"]] = WeightSpec((self.kv_rank,), init="norm")
@@ -105,15 +116,15 @@ class LatentAttention(Mixer):
 
     def bind(self, weights) -> None:
         H, n = self.num_heads, self.names
-        mats = [weights[n["dq"]]] + ([] if self.kv_shared else [weights[n["dkv"]]])
+        mats = [weights[n["dq"] if self.q_rank else n["q"]]] + ([] if self.kv_shared else [weights[n["dkv"]]])
         if len({m.dtype for m in mats}) != 1:
             raise ConfigError(f"{self.prefix}: the down projections are stored in different dtypes")
         # both down projections read the same input: one product [dq | c | r]
         self.down = Linear(torch.cat(mats, dim=0) if len(mats) > 1 else mats[0], self.rt)
-        self.uq = Linear(weights[n["uq"]], self.rt)
+        self.uq = Linear(weights[n["uq"]], self.rt) if self.q_rank else None
         self.o = Linear(weights[n["o"]], self.rt)
         act = self.rt.dtype
-        self.q_norm = weights[n["dq_norm"]].to(act).contiguous()
+        self.q_norm = weights[n["dq_norm"]].to(act).contiguous() if self.q_rank else None
         self.kv_norm = None if self.kv_shared else weights[n["dkv_norm"]].to(act).contiguous()
         # per head: W_uk,h^T [kv_rank, dim] takes a query into latent space, W_uv,h [vdim, kv_rank] a
         # weighted sum of latents to the head's output
@@ -121,7 +132,7 @@ class LatentAttention(Mixer):
         self.uv = weights[n["uv"]].view(H, self.vdim, self.kv_rank).contiguous()
 
     def weight_bytes(self) -> int:
-        return self.down.nbytes + self.uq.nbytes + self.o.nbytes \
+        return self.down.nbytes + (self.uq.nbytes if self.uq is not None else 0) + self.o.nbytes \
             + (self.uk_t.numel() + self.uv.numel()) * self.uk_t.element_size()
 
     # ---- the step -----------------------------------------------------------
@@ -133,17 +144,27 @@ class LatentAttention(Mixer):
         tables = ctx.block_tables[cache.group]
         pool = cache.k_pool
         lat = self.down(x)
-        cq = torch.empty((N, self.q_rank), dtype=x.dtype, device=x.device)
-        core.latent_prepare(lat, self.q_rank, self.kv_rank, self.rot_dim, self.rotary_dim, self.q_norm,
-                            self.kv_norm, self.eps, self.inv_freq, ctx.positions, ctx.row_entry,
-                            tables if writes else None, cq, pool if writes else None, self.rt.err)
-        q = self.uq(cq)
+        if self.q_rank:
+            cq = torch.empty((N, self.q_rank), dtype=x.dtype, device=x.device)
+            core.latent_prepare(lat, self.q_rank, self.kv_rank, self.rot_dim, self.rotary_dim, self.q_norm,
+                                self.kv_norm, self.eps, self.inv_freq, ctx.positions, ctx.row_entry,
+                                tables if writes else None, cq, pool if writes else None, self.rt.err,
+                                adjacent=self.adjacent, magnitude=self.magnitude)
+            q = self.uq(cq)
+        else:
+            # the product's rows are [ q | c | r ]: the queries are used as they are
+            hq = H * (self.dim + self.rot_dim)
+            q = lat[:, :hq]
+            if writes:
+                core.latent_prepare(lat[:, hq:], 0, self.kv_rank, self.rot_dim, self.rotary_dim, None, self.kv_norm,
+                                    self.eps, self.inv_freq, ctx.positions, ctx.row_entry, tables, None, pool,
+                                    self.rt.err, adjacent=self.adjacent, magnitude=self.magnitude)
         # queries in latent space and the sums of latents are kept head by head ([H, N, .]):
         # the per-head products then read and write plain matrices
         q_abs = torch.empty((H, N, W), dtype=x.dtype, device=x.device)
         core.latent_q_rotate(q, H, self.dim, self.rot_dim, self.rotary_dim, self.inv_freq, ctx.positions,
-                             q_abs.transpose(0, 1), self.kv_rank)
-        q3 = q.view(N, H, self.dim + self.rot_dim)
+                             q_abs.transpose(0, 1), self.kv_rank, adjacent=self.adjacent, magnitude=self.magnitude)
+        q3 = q.unflatten(1, (H, self.dim + self.rot_dim))
         batched_matmul_nt(q3[:, :, : self.dim].transpose(0, 1), self.uk_t, q_abs[:, :, : self.kv_rank])
         o_lat = torch.empty((H, N, self.kv_rank), dtype=x.dtype, device=x.device)
         attn_ops.latent_attention(q_abs.transpose(0, 1), pool, o_lat.transpose(0, 1), self.kv_rank, ctx, tables,

@@ -24,7 +24,16 @@ are ``sigmoid(z)``, the ``top`` largest are chosen and are the weights as they
 are (``renormalize``: divided by their sum); with ``groups`` ({"count", "keep",
 "top": 2}) expert e belongs to group ``e // (experts // count)``, a group is
 scored by the sum of the ``top`` largest scores in it, and the experts outside
-the ``keep`` best-scored groups are struck out before the choice.
+the ``keep`` best-scored groups are struck out before the choice;
+"softmax_all": the router has ``experts + identity`` outputs, the scores are the
+softmax over all of them, the ``top`` largest ``score + correction`` (a tensor,
+name in ``correction``, or None) are chosen, and their weights are the scores
+without the correction over the chosen ones' sum (+ 1e-20); the last
+``identity`` outputs have no expert and no tensors: choosing one adds the
+weight times the token's input.  ``shared`` ({"size", "prefix", "gate"}): one more
+gated feed-forward that every token uses, added times ``sigmoid(w_gate . x)``
+(one number per token; ``gate`` names the [1, hidden] tensor behind the shared
+expert's prefix, None: no gate).
 """
 
 from __future__ import annotations
@@ -47,8 +56,9 @@ class MixtureOfExperts(FeedForward):
         self.expert_size = int(params["expert_size"])
         self.experts = int(params["experts"])
         self.top = int(params["top"])
-        if not 0 < self.top <= self.experts:
-            raise ConfigError(f"mixture of experts: top {self.top} must be within 1..{self.experts}")
+        if not 0 < self.top <= self.experts + int(params.get("identity") or 0):
+            raise ConfigError(f"mixture of experts: top {self.top} must be within 1..{self.experts} (+ the outputs "
+                              f"without an expert)")
         self.activation = params.get("activation", "silu")
         if self.activation not in core.ACTIVATIONS:
             raise ConfigError(f"mixture of experts: unknown activation {self.activation!r}")
@@ -58,8 +68,20 @@ class MixtureOfExperts(FeedForward):
         bias = params.get("router_bias", "router.b")
         self.bias_name = self.prefix + bias if bias else None
         self.scoring = params.get("scoring", "softmax_top")
-        if self.scoring not in ("softmax_top", "sigmoid"):
-            raise ConfigError(f"mixture of experts: unknown scoring {self.scoring!r} (softmax_top, sigmoid)")
+        if self.scoring not in ("softmax_top", "sigmoid", "softmax_all"):
+            raise ConfigError(f"mixture of experts: unknown scoring {self.scoring!r} (softmax_top, sigmoid, "
+                              f"softmax_all)")
+        self.identity = int(params.get("identity") or 0)
+        corr = params.get("correction")
+        self.correction_name = self.prefix + corr if corr else None
+        shared = params.get("shared")
+        self.shared = None
+        if shared:
+            self.shared = {"size": int(shared["size"]), "prefix": self.prefix + shared.get("prefix", "shared."),
+                           "gate": shared.get("gate")}
+        if (self.identity or self.correction_name or self.shared) and self.scoring != "softmax_all":
+            raise ConfigError("mixture of experts: outputs without an expert, a correction of the choice and an "
+                              "expert for every token go with softmax_all scoring")
         self.renormalize = bool(params.get("renormalize", False))
         groups = params.get("groups") or {}
         self.group_count = int(groups.get("count", 1))
@@ -84,9 +106,17 @@ class MixtureOfExperts(FeedForward):
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         h, f = self.hidden_size, self.expert_size
-        specs = {self.router_name: WeightSpec((self.experts, h), std=0.5)}
+        specs = {self.router_name: WeightSpec((self.experts + self.identity, h), std=0.5)}
         if self.bias_name:
             specs[self.bias_name] = WeightSpec((self.experts,), std=0.5)
+        if self.correction_name:
+            specs[self.correction_name] = WeightSpec((self.experts + self.identity,), std=0.02)
+        if self.shared:
+            sp, sf = self.shared["prefix"], self.shared["size"]
+            specs[sp + "gate"], specs[sp + "up"], specs[sp + "down"] = WeightSpec((sf, h)), WeightSpec((sf, h)), \
+                WeightSpec((h, sf))
+            if self.shared["gate"]:
+                specs[sp + self.shared["gate"]] = WeightSpec((1, h), std=0.3)
         for e in range(self.experts):
             specs[self._name(e, "gate")] = WeightSpec((f, h))
             specs[self._name(e, "up")] = WeightSpec((f, h))
@@ -114,19 +144,38 @@ class MixtureOfExperts(FeedForward):
         # the router is 32-bit arithmetic whatever the engine's dtype
         self.router = weights[self.router_name].contiguous()
         self.router_bias = weights[self.bias_name].to(torch.float32).contiguous() if self.bias_name else None
+        self.correction = weights[self.correction_name].to(torch.float32).contiguous() if self.correction_name else None
+        self.shared_ffn = None
+        if self.shared:
+            from .mlp import SwiGLU
+
+            sp = self.shared["prefix"]
+            self.shared_ffn = SwiGLU({"hidden_size": h, "intermediate_size": self.shared["size"], "prefix": sp,
+                                      "names": {"gate": "gate", "up": "up", "down": "down"},
+                                      "activation": self.activation}, self.rt)
+            self.shared_ffn.bind(weights)
+            if self.shared["gate"]:
+                # the gate's logit is one more row of the router's product
+                self.router = torch.cat([self.router, weights[sp + self.shared["gate"]].to(self.router.dtype)],
+                                        dim=0).contiguous()
 
     def weight_bytes(self) -> int:
-        return self.gate_up.nbytes + self.down.nbytes + self.router.numel() * self.router.element_size()
+        return self.gate_up.nbytes + self.down.nbytes + self.router.numel() * self.router.element_size() \
+            + (self.shared_ffn.weight_bytes() if self.shared_ffn is not None else 0)
 
     def route(self, x: torch.Tensor):
         """(ids [N, top] int32, weights [N, top] float32, gate [N, experts] float32)."""
         n, dev = x.shape[0], x.device
-        logits = torch.empty((n, self.experts), dtype=torch.float32, device=dev)
+        logits = torch.empty((n, self.router.shape[0]), dtype=torch.float32, device=dev)
         core.router_logits(x, self.router, logits)  # 32-bit multiply-adds, a fixed order per row
         ids = torch.empty((n, self.top), dtype=torch.int32, device=dev)
         wts = torch.empty((n, self.top), dtype=torch.float32, device=dev)
         gate = torch.empty((n, self.experts), dtype=torch.float32, device=dev)
-        if self.scoring == "sigmoid":
+        if self.scoring == "softmax_all":
+            self._extra = torch.empty((n, 2), dtype=torch.float32, device=dev)
+            core.moe_route_softmax_all(logits, self.correction, self.experts + self.identity, self.experts, self.top,
+                                       ids, wts, gate, self._extra)
+        elif self.scoring == "sigmoid":
             core.moe_route_scored(logits, self.router_bias, self.top, ids, wts, gate, groups=self.group_count,
                                   keep=self.group_keep, group_top=self.group_top, renorm=self.renormalize)
         else:
@@ -146,4 +195,11 @@ class MixtureOfExperts(FeedForward):
         if not fused:
             core.gated_act(self.gate_up(x), act, self.activation, block=self.block, scale=gate,
                            cols_per_scale=self.expert_size)
-        return self.down(act)
+        routed = self.down(act)
+        if self.scoring != "softmax_all" or not (self.identity or self.shared_ffn is not None):
+            return routed
+        # the input handed on by the outputs without an expert, and the expert that every token uses
+        shared = self.shared_ffn.forward(x, ctx) if self.shared_ffn is not None else None
+        out = torch.empty_like(routed)
+        core.moe_combine(routed, x, shared, self._extra, out)
+        return out

@@ -148,6 +148,8 @@ class PartRMSNorm(Norm):
     ``slot`` and the stream becomes ``sum_{j <= slot} coef[j] results[j]`` - in one
     kernel, which also writes the stream's rounding to the activation dtype.
 
+    ``add_gated(stream, y, gate, bias, mult)``: ``x + mult * norm(y * sigmoid(gate + bias))``.
+
     Parameters: ``hidden_size``, ``eps``, ``parts`` (default 1), ``weight``.
     """
 
@@ -192,7 +194,26 @@ class PartRMSNorm(Norm):
         stream.residual = out
         stream.act = out if act is None else act
 
+    def add_gated(self, stream: ResidualStream, y: torch.Tensor, gate: Optional[torch.Tensor],
+                  gate_bias: Optional[torch.Tensor], mult: float = 1.0) -> None:
+        """The stream becomes ``x + mult * norm(y * sigmoid(gate + gate_bias))`` (``gate``
+        None: ``norm(y)``), in place and in 32-bit; no activation copy is made."""
+        if stream.pending is not None:
+            stream.flush()
+        x = stream.residual
+        # (the embedding's output, when the stream keeps it, is never written over)
+        out = torch.empty_like(x) if stream.origin is not None and stream.origin.data_ptr() == x.data_ptr() else x
+        core.gated_norm_add(x, y, gate, gate_bias, self.weight, self.parts, self.eps, mult, out)
+        stream.residual = out
+        stream.act = None
+
     def apply(self, x: torch.Tensor) -> torch.Tensor:
         out = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+        core.part_rmsnorm(x, self.weight, self.parts, self.eps, out)
+        return out
+
+    def apply_f32(self, x: torch.Tensor) -> torch.Tensor:
+        """The norm of 32-bit rows, returned in 32-bit."""
+        out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
         core.part_rmsnorm(x, self.weight, self.parts, self.eps, out)
         return out

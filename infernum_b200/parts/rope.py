@@ -16,6 +16,15 @@ The reference has this ramp only in its YaRN branch with fixed bounds and an
 extra magnitude factor (infernum/src/rope.rs:91-120); llama3 has no magnitude
 factor.
 
+``scaling`` of type "ramp" divides the frequencies by ``factor`` along a linear
+ramp over the pair index j: with ``D(t) = rd ln(P / (2 pi t)) / (2 ln theta)`` the
+index of the pair that makes t turns over the original context P,
+``lo = max(floor(D(fast)), 0)``, ``hi = min(ceil(D(slow)), rd - 1)``,
+``r_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1)``, ``f'_j = r_j f_j / factor +
+(1 - r_j) f_j``; cosine and sine are then multiplied by ``0.1 ln(factor) + 1``
+(``rotary_magnitude``).  The reference has this in its YaRN branch
+(infernum/src/rope.rs:91-120).
+
 Parameters: ``head_dim``, ``rotary_dim`` (default: head_dim), ``theta``,
 ``scaling`` (None or a dict with rope_type, factor, low_freq_factor,
 high_freq_factor, original_max_position_embeddings).
@@ -41,8 +50,21 @@ def rotary_inv_freq(rotary_dim: int, theta: float, scaling: Optional[Dict[str, A
     kind = scaling.get("rope_type", scaling.get("type"))
     if kind in (None, "default"):
         return freqs
+    if kind == "ramp":
+        factor, orig = float(scaling["factor"]), float(scaling["original"])
+
+        def pair_of(turns: float) -> float:
+            return rotary_dim * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+        lo = max(math.floor(pair_of(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(pair_of(float(scaling["slow"]))), rotary_dim - 1)
+        out = []
+        for j, f in enumerate(freqs):
+            r = min(max((j - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f / factor * r + f * (1.0 - r))
+        return out
     if kind != "llama3":
-        raise ConfigError(f"rotary scaling {kind!r} is not supported (supported: llama3)")
+        raise ConfigError(f"rotary scaling {kind!r} is not supported (supported: llama3, ramp)")
     factor = float(scaling["factor"])
     low = float(scaling["low_freq_factor"])
     high = float(scaling["high_freq_factor"])
@@ -58,6 +80,13 @@ def rotary_inv_freq(rotary_dim: int, theta: float, scaling: Optional[Dict[str, A
             m = (orig / wavelen - low) / (high - low)
             out.append((1.0 - m) * f / factor + m * f)
     return out
+
+
+def rotary_magnitude(scaling: Optional[Dict[str, Any]]) -> float:
+    """What cosine and sine are multiplied by: 1, or ``0.1 ln(factor) + 1`` for "ramp" scaling."""
+    if scaling and scaling.get("rope_type", scaling.get("type")) == "ramp":
+        return 0.1 * math.log(float(scaling["factor"])) + 1.0
+    return 1.0
 
 
 @POSITION_ENCODINGS.register("rotary")

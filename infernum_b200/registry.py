@@ -70,3 +70,5 @@ def _ensure_builtin() -> None:
         from .models import nadozen  # noqa: F401
     if "Bolovik" not in _ARCHITECTURES:
         from .models import bolovik  # noqa: F401
+    if "Vodatar" not in _ARCHITECTURES:
+        from .models import vodatar  # noqa: F401
