@@ -147,12 +147,12 @@ class VodatarMlpConfig:
         if kind != "moe":
             raise ConfigError(f"config.json: {where}kind {kind!r} is not supported (moe)")
         router = _section(d, "router", where)
-        experts, top = take_int(router, "experts", minimum=0), take_int(router, "top")
+        experts, top = take_int(router, "experts"), take_int(router, "top")
         identity = take_int(router, "identity", default=0, minimum=0)
         if top > experts + identity:
             raise ConfigError(f"config.json: {where}router.top {top} exceeds the {experts + identity} router outputs")
         shared = _section(d, "shared", where, optional=True)
-        return cls(ff=take_int(_section(d, "expert", where), "ff") if experts else 0, experts=experts, top=top,
+        return cls(ff=take_int(_section(d, "expert", where), "ff"), experts=experts, top=top,
                    identity=identity, shared_ff=take_int(shared, "ff") if shared is not None else 0)
 
 

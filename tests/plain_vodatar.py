@@ -148,37 +148,43 @@ def gated_expert(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str) -> torch.T
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def route(h: torch.Tensor, router: Dict, w: Dict[str, torch.Tensor], p: str):
+def route(h: torch.Tensor, router: Dict, w: Dict[str, torch.Tensor], p: str, margins_out: Optional[list] = None):
     """(ids [T, top], weights [T, top]) over ``experts + identity`` outputs: softmax
     over all of them, the choice by score + correction (lowest index among equals),
-    the weights the chosen scores over their sum."""
+    the weights the chosen scores over their sum.  ``margins_out`` collects, per
+    token, by how much the last chosen output beat the best one left out."""
     z = h @ w[p + "router"].T
     s = torch.softmax(z, dim=-1)
     choice = s + w[p + "correction"] if (p + "correction") in w else s
     top = int(router["top"])
-    ids = torch.sort(choice, dim=-1, descending=True, stable=True).indices[:, :top]
+    order = torch.sort(choice, dim=-1, descending=True, stable=True)
+    ids = order.indices[:, :top]
+    if margins_out is not None:
+        margins_out.append(order.values[:, top - 1] - order.values[:, top] if top < choice.shape[1]
+                           else torch.full((h.shape[0],), float("inf"), dtype=h.dtype))
     chosen = torch.gather(s, 1, ids)
     return ids, chosen / (chosen.sum(dim=-1, keepdim=True) + 1e-20)
 
 
-def mixture(h: torch.Tensor, mlp: Dict, w: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
+def mixture(h: torch.Tensor, mlp: Dict, w: Dict[str, torch.Tensor], p: str, margins_out: Optional[list] = None) -> torch.Tensor:
     router = mlp["router"]
     E, I = int(router["experts"]), int(router.get("identity", 0))
-    ids, wts = route(h, router, w, p)
+    ids, wts = route(h, router, w, p, margins_out)
     out = torch.zeros_like(h)
-    for t in range(h.shape[0]):
-        for e, a in zip(ids[t].tolist(), wts[t]):
-            if e >= E:  # an identity expert hands its input on
-                out[t] += a * h[t]
-            else:
-                out[t] += a * gated_expert(h[t: t + 1], w, f"{p}e{e}.")[0]
+    for e in range(E + I):
+        share = (wts * (ids == e)).sum(dim=-1, keepdim=True)  # [T, 1], 0 where the token did not choose e
+        if float(share.abs().sum()) == 0.0:
+            continue
+        # an output without an expert hands its input on
+        out = out + share * (h if e >= E else gated_expert(h, w, f"{p}e{e}."))
     if mlp.get("shared"):
         gate = torch.sigmoid(h @ w[p + "shared.sg"].T)  # [T, 1]
         out = out + gate * gated_expert(h, w, p + "shared.")
     return out
 
 
-def layer(x: torch.Tensor, spec: Dict, cfg: Dict, w: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
+def layer(x: torch.Tensor, spec: Dict, cfg: Dict, w: Dict[str, torch.Tensor], p: str,
+          margins_out: Optional[list] = None) -> torch.Tensor:
     eps, parts, mult = float(cfg["norm"]["eps"]), int(cfg["norm"].get("groups", 1)), float(cfg.get("residual_mult", 1.0))
     canon = cfg.get("canon") or {}
 
@@ -195,7 +201,7 @@ def layer(x: torch.Tensor, spec: Dict, cfg: Dict, w: Dict[str, torch.Tensor], p:
     else:
         x = sub(x, 1, lambda u: latent_attention(u, spec["mixer"], w, p + "mix.", eps))
     if spec.get("mlp"):
-        x = sub(x, 2, lambda u: mixture(u, spec["mlp"], w, p + "mlp."))
+        x = sub(x, 2, lambda u: mixture(u, spec["mlp"], w, p + "mlp.", margins_out))
     return x
 
 
@@ -212,7 +218,8 @@ def run_order(cfg: Dict):
     return order + [(i, None) for i in range(b, L)]
 
 
-def forward(tokens, cfg: Dict, weights: Dict[str, torch.Tensor], dtype=F, keep_layers: bool = False):
+def forward(tokens, cfg: Dict, weights: Dict[str, torch.Tensor], dtype=F, keep_layers: bool = False,
+            margins_out: Optional[list] = None):
     """Logits [T, vocab] of one sequence; with ``keep_layers`` also the stream after every run."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps, parts = float(cfg["norm"]["eps"]), int(cfg["norm"].get("groups", 1))
@@ -222,7 +229,56 @@ def forward(tokens, cfg: Dict, weights: Dict[str, torch.Tensor], dtype=F, keep_l
     for i, begins in run_order(cfg):
         if begins is not None:
             x = torch.cat([x, x0], dim=-1) @ w["loop.in"].T + w["loop.step"][begins]
-        x = layer(x, cfg["layers"][i], cfg, w, f"l{i}.")
+        x = layer(x, cfg["layers"][i], cfg, w, f"l{i}.", margins_out)
         kept.append(x)
     logits = part_norm(x, w["final.norm"], parts, eps) @ w["head"].T
     return (logits, torch.stack(kept)) if keep_layers else logits
+
+
+def argmax(logits: torch.Tensor) -> int:
+    """The lowest index among the largest values."""
+    return int((logits == logits.max()).nonzero()[0])
+
+
+def read_config(folder_or_dict) -> dict:
+    import json
+    import os
+
+    if isinstance(folder_or_dict, dict):
+        return folder_or_dict
+    with open(os.path.join(folder_or_dict, "config.json")) as fh:
+        return json.load(fh)
+
+
+def read_weights(folder: str) -> Dict[str, torch.Tensor]:
+    import os
+
+    from safetensors.torch import load_file
+
+    return {k: (v.to(F) if v.is_floating_point() else v) for k, v in
+            load_file(os.path.join(folder, "model.safetensors")).items()}
+
+
+class Plain:
+    """The plain implementation over a model folder, logits cached by sequence."""
+
+    def __init__(self, folder: Optional[str], config: Optional[dict] = None, weights=None):
+        self.cfg = read_config(folder if folder is not None else config)
+        self.weights = read_weights(folder) if folder is not None else weights
+        self._cache: Dict[tuple, torch.Tensor] = {}
+        self._margins: Dict[tuple, torch.Tensor] = {}
+
+    def logits(self, tokens) -> torch.Tensor:
+        key = tuple(tokens)
+        if key not in self._cache:
+            margins: list = []
+            with torch.no_grad():
+                self._cache[key] = forward(list(tokens), self.cfg, self.weights, margins_out=margins).to(torch.float32)
+            self._margins[key] = torch.stack(margins).min(0).values if margins else \
+                torch.full((len(key),), float("inf"))
+        return self._cache[key]
+
+    def margins(self, tokens) -> torch.Tensor:
+        """Per position the smallest routing margin over all runs of layers."""
+        self.logits(tokens)
+        return self._margins[tuple(tokens)]
