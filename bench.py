@@ -435,6 +435,59 @@ def bolovik_prefill_flops(cfg: dict, T: int) -> float:
     return total + 2.0 * D * cfg["vocab"]
 
 
+def vodatar_config(width, layers, heads, kv_heads, ff, vocab, experts=16, top=4, identity=2):
+    """Layers in fours: attention through a latent (heads of 128 + 64 rotated, values of 128, a latent of
+    512, frequencies on a ramp), then three layers of differential attention (half the heads, two maps
+    of 128 each, values of 256, a convolution of 4 taps, scores capped at 50); every layer with a
+    mixture of experts whose chosen experts do half a dense layer's work (an expert has ff / (2 top)
+    columns; two more router outputs hand the input on) beside a shared expert that does the other
+    half.  The first two layers are walked twice, so ``layers`` runs come from ``layers - 2`` layers."""
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+           "rot": {"dims": 64, "base": 10000.0,
+                   "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    att = {"heads": max(1, heads // 2), "kv_heads": max(1, kv_heads // 2), "dim": 128, "vdim": 256,
+           "scale": 128 ** -0.5, "softcap": 50.0, "diff": 0.3, "conv": 4, "rot": {"dims": 128, "base": 500000.0}}
+    moe = {"kind": "moe", "expert": {"ff": ff // (2 * top)},
+           "router": {"experts": experts, "top": top, "identity": identity}, "shared": {"ff": ff // 2}}
+    n = max(layers - 2, 2)
+    out = [{"type": "latent_attention" if i % 4 == 0 else "attention", "mixer": lat if i % 4 == 0 else att, "mlp": moe}
+           for i in range(n)]
+    return {"architecture": "Vodatar", "vocab": vocab, "width": width, "residual_mult": 0.7,
+            "norm": {"eps": 1e-6, "groups": 4}, "canon": {"taps": 3}, "loop": {"start": 0, "stop": 2, "times": 2},
+            "layers": out, "max_position": 8192}
+
+
+def vodatar_prefill_flops(cfg: dict, T: int) -> float:
+    """Multiply-adds x 2 of one prompt step: the products of every run of a layer (a token's chosen
+    experts only, the shared expert, the gates of both sub-layers, the product that re-enters a pass),
+    attention in latent space as the engine computes it, and both score maps over the keys a query sees."""
+    D, total = cfg["width"], 0.0
+    keys = T * (T + 1) / 2.0
+    loop = cfg.get("loop")
+    runs = list(range(len(cfg["layers"])))
+    if loop:
+        runs = list(range(loop["start"])) + list(range(loop["start"], loop["stop"])) * loop["times"] \
+            + list(range(loop["stop"], len(cfg["layers"])))
+        total += 2.0 * T * D * 2 * D * loop["times"]
+    for i in runs:
+        layer = cfg["layers"][i]
+        m = layer["mixer"]
+        if layer["type"] == "attention":
+            H, G, d, v = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            total += 2.0 * T * D * (H * 2 * d + G * 2 * d + G * v) + 2.0 * T * H * v * D + 2.0 * H * (2 * d + 2 * v) * keys
+        else:
+            H, d, r, v, kr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            total += 2.0 * T * D * (H * (d + r) + kr + r) + 2.0 * T * H * (d + v) * kr + 2.0 * T * H * v * D \
+                + 2.0 * H * (2 * kr + r) * keys
+        total += 2.0 * T * D * D  # the mixer's gate
+        mlp = layer.get("mlp")
+        if mlp:
+            r = mlp["router"]
+            total += 6.0 * T * D * mlp["expert"]["ff"] * r["top"] + 2.0 * T * D * (r["experts"] + r.get("identity", 0)) \
+                + 6.0 * T * D * (mlp.get("shared") or {}).get("ff", 0) + 2.0 * T * D * D
+    return total + 2.0 * D * cfg["vocab"]
+
+
 DESIGN_SIZES = {
     # name: (width, layers, heads, feed-forward, vocabulary, q_rank, llama kv heads)
     "2b-shape": (2048, 8, 16, 8192, 32000, 768, 4),
@@ -445,7 +498,8 @@ DESIGN_SIZES = {
 def design_compare(args, peaks) -> dict:
     """Prefill and decode of the chosen design at a few sizes, and of the decoder it is set beside
     (the Llama decoder; for Bolovik the Nadozen decoder, whose layers also alternate window
-    attention and a recurrent state) at the same width, depth, heads, feed-forward width and
+    attention and a recurrent state; for Vodatar the Rugesun decoder, which also has attention
+    through a latent and mixtures of experts) at the same width, depth, heads, feed-forward width and
     vocabulary."""
     import gc
 
@@ -473,6 +527,11 @@ def design_compare(args, peaks) -> dict:
             other_flops = bolovik_prefill_flops
             beside, beside_cfg, beside_flops = "nadozen", nadozen_config(width, layers, heads, kv_heads, ff, vocab), \
                 nadozen_prefill_flops
+        elif args.design == "vodatar":
+            other = vodatar_config(width, layers, heads, kv_heads, ff, vocab)
+            other_flops = vodatar_prefill_flops
+            beside, beside_cfg, beside_flops = "rugesun", rugesun_config(width, layers, heads, ff, vocab, q_rank), \
+                rugesun_prefill_flops
         else:
             other = rugesun_config(width, layers, heads, ff, vocab, q_rank)
             other_flops = rugesun_prefill_flops
@@ -592,9 +651,9 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print its numbers (for profiling)")
     ap.add_argument("--no-cuda-graph", action="store_true", help="launch decode steps kernel by kernel")
-    ap.add_argument("--design", choices=["rugesun", "nadozen", "bolovik"], default=None,
+    ap.add_argument("--design", choices=["rugesun", "nadozen", "bolovik", "vodatar"], default=None,
                     help="instead of the default workload: prefill and decode of this design at a few sizes,\n"
-                         "beside the Llama decoder (bolovik: the Nadozen decoder) at equal sizes; prints one JSON line {\"design\": ...}")
+                         "beside the Llama decoder (bolovik: the Nadozen decoder; vodatar: the Rugesun decoder) at equal sizes; prints one JSON line {\"design\": ...}")
     ap.add_argument("--size", default=None, help="with --design: one of its sizes only")
     ap.add_argument("--only-model", default=None, help="with --design: the design's name, or the name of the one beside it, only")
     args = ap.parse_args()

@@ -1,0 +1,336 @@
+// Differential attention on the tensor cores (bf16 mma.sync m16n8k16), for prompts and decoded
+// tokens alike.  Compiled per (DIFF_D, DIFF_E): the size of one score map and of a value.
+//
+//   o(i) = sum_j w(i, j) v(j),   w = softmax(s_1)(i, j) - lambda * softmax(s_2)(i, j),   j <= i
+//   s_m = cap * tanh(q_m . k_m * scale / cap);   out = o / sqrt(mean(o^2) + eps) * out_scale
+//
+// The two maps have their own maxima and denominators, so two accumulators would be the
+// straight way; with values twice as wide as a map they do not fit a warp's registers.  The
+// kernel walks the keys twice instead: the first walk computes both maps' scores and keeps
+// only each row's two maxima and denominators; the second computes the scores again, forms
+// the final signed weights w (32-bit, rounded to bf16 for the product as the package's other
+// bf16 attention kernels round their probabilities) and accumulates one product w V.  The
+// multiply-adds are the same as with two accumulators (two score products more, one value
+// product less), the keys are read twice.
+//
+// A CTA (four warps) takes 64 packed rows - (query row, head of the group) pairs that share a
+// key/value head - of one entry; a warp 16 of them.  Keys come in tiles of 32 that start at
+// absolute multiples of 32 whatever the step's cut, through the block table, by cp.async into
+// padded shared memory; rows beyond the last key any row of the CTA sees are zero-filled, so
+// what an earlier user left in a page never meets a zero weight.
+#include "common.cuh"
+
+using namespace ib;
+
+#ifndef DIFF_D
+#define DIFF_D 128
+#endif
+#ifndef DIFF_E
+#define DIFF_E 256
+#endif
+
+namespace {
+constexpr int D = DIFF_D, E = DIFF_E, KW = 2 * DIFF_D;
+constexpr int BM = 64, BN = 32, WARPS = 4, THREADS = WARPS * 32;
+constexpr int QS = KW + 8, KS = KW + 8, VS = E + 8;  // row strides in shared memory (elements): 16 bytes of padding
+constexpr int NT_E = E / 8;                          // accumulator tiles of 8 columns
+static_assert(D % 16 == 0 && E % 16 == 0 && D >= 16 && E >= 16 && E <= 256 && D <= 256, "sizes this kernel takes");
+
+__device__ __forceinline__ void ldsm_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const bf16* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const bf16* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+}
+__device__ __forceinline__ void cp_async16(bf16* smem, const bf16* gmem) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(a), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+
+// One tile of keys (and, with_v, values) into shared memory; rows of keys beyond `last_key` are zeros.
+__device__ __forceinline__ void load_tile(bf16* ks, bf16* vs, const bf16* __restrict__ k_pool,
+                                          const bf16* __restrict__ v_pool, const int* __restrict__ table, int max_blocks,
+                                          int j0, int last_key, int g, int nkv, int page_size, int num_pages,
+                                          bool with_v, unsigned* err) {
+    constexpr int KC = KW / 8, VC = E / 8;  // 16-byte chunks in a row
+    for (int c = threadIdx.x; c < BN * KC; c += THREADS) {
+        const int key = c / KC, part = c % KC, j = j0 + key;
+        bf16* dst = ks + key * KS + part * 8;
+        int page = -1;
+        if (j <= last_key) {
+            page = j / page_size < max_blocks ? table[j / page_size] : -1;
+            if (page < 0 || page >= num_pages) {
+                if (part == 0) atomicOr(err, IB_FLAG_BAD_PAGE);
+                page = -1;
+            }
+        }
+        if (page >= 0)
+            cp_async16(dst, k_pool + (((size_t)page * nkv + g) * page_size + (j % page_size)) * KW + part * 8);
+        else
+            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    if (with_v) {
+        for (int c = threadIdx.x; c < BN * VC; c += THREADS) {
+            const int key = c / VC, part = c % VC, j = j0 + key;
+            bf16* dst = vs + key * VS + part * 8;
+            int page = -1;
+            if (j <= last_key) {
+                page = j / page_size < max_blocks ? table[j / page_size] : -1;
+                if (page < 0 || page >= num_pages) page = -1;
+            }
+            if (page >= 0)
+                cp_async16(dst, v_pool + (((size_t)page * nkv + g) * page_size + (j % page_size)) * E + part * 8);
+            else
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+// Both maps' scores of a warp's 16 rows against the tile's 32 keys: s[map][tile of 8 keys][4].
+__device__ __forceinline__ void scores(float (&s)[2][4][4], const bf16* qs_warp, const bf16* ks, int lane) {
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[m][n][i] = 0.f;
+    const int a_row = lane & 15, a_col = (lane >> 4) * 8;
+    const int b_key = ((lane >> 4) * 8) + (lane & 7), b_col = ((lane >> 3) & 1) * 8;
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+#pragma unroll 4
+        for (int kk = 0; kk < D / 16; ++kk) {
+            unsigned a[4];
+            ldsm_x4(a[0], a[1], a[2], a[3], qs_warp + a_row * QS + m * D + kk * 16 + a_col);
+#pragma unroll
+            for (int pr = 0; pr < 2; ++pr) {
+                unsigned b0, b1, b2, b3;
+                ldsm_x4(b0, b1, b2, b3, ks + (pr * 16 + b_key) * KS + m * D + kk * 16 + b_col);
+                mma_bf16(s[m][2 * pr], a, b0, b1);
+                mma_bf16(s[m][2 * pr + 1], a, b2, b3);
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ float capped(float s, float scale, float cap, float inv_cap) {
+    s *= scale;
+    return cap > 0.f ? cap * tanhf(s * inv_cap) : s;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                          bf16* __restrict__ out, const int* __restrict__ cu_rows, const int* __restrict__ positions,
+                          const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int page_size,
+                          int num_pages, float scale, float cap, float lambda, float eps, float out_scale,
+                          unsigned* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* qs = reinterpret_cast<bf16*>(smem_raw);
+    bf16* ks = qs + BM * QS;
+    bf16* vs = ks + BN * KS;
+    const int en = blockIdx.y, g = blockIdx.z;
+    const int R = nh / nkv;
+    const int row0 = cu_rows[en], n_rows = cu_rows[en + 1] - row0;
+    const int n_packed = n_rows * R;
+    const int tile0 = blockIdx.x * BM;
+    if (tile0 >= n_packed) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gq = lane >> 2, tq = lane & 3;
+    const int* table = block_tables + (size_t)en * max_blocks;
+    const int pos0 = positions[row0];  // an entry's rows are consecutive positions
+    const int packed_here = min(BM, n_packed - tile0);
+    const int last_key = pos0 + (tile0 + packed_here - 1) / R;  // what the CTA's last row sees
+
+    // queries: packed row p = (row p / R, head g R + p % R), both maps side by side
+    {
+        constexpr int QC = KW / 8;
+        for (int c = threadIdx.x; c < BM * QC; c += THREADS) {
+            const int r = c / QC, part = c % QC, p = tile0 + r;
+            bf16* dst = qs + r * QS + part * 8;
+            if (p < n_packed)
+                cp_async16(dst, q + ((size_t)(row0 + p / R) * nh + g * R + p % R) * KW + part * 8);
+            else
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+    }
+    const bf16* qs_warp = qs + warp * 16 * QS;
+    const int p_lo = tile0 + warp * 16 + gq, p_hi = p_lo + 8;
+    const int pos_lo = p_lo < n_packed ? pos0 + p_lo / R : -1, pos_hi = p_hi < n_packed ? pos0 + p_hi / R : -1;
+    const int warp_last = min(tile0 + warp * 16 + 15, n_packed - 1);
+    const int warp_last_key = tile0 + warp * 16 < n_packed ? pos0 + warp_last / R : -1;  // -1: the warp has no row
+    const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+
+    // ---- first walk: maxima and denominators of both maps
+    float mx[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, den[2][2] = {{0.f, 0.f}, {0.f, 0.f}};  // [map][lo, hi]
+    for (int j0 = 0; j0 <= last_key; j0 += BN) {
+        __syncthreads();  // the tile before is done with
+        load_tile(ks, vs, k_pool, v_pool, table, max_blocks, j0, last_key, g, nkv, page_size, num_pages, false, err);
+        cp_async_wait_all();
+        __syncthreads();
+        if (j0 > warp_last_key) continue;  // (the whole warp)
+        float s[2][4][4];
+        scores(s, qs_warp, ks, lane);
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            float t_lo = -INFINITY, t_hi = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int j = j0 + n * 8 + 2 * tq + (i & 1);
+                    const bool hi = i >= 2;
+                    const float v = j <= (hi ? pos_hi : pos_lo) ? capped(s[m][n][i], scale, cap, inv_cap) : -INFINITY;
+                    s[m][n][i] = v;
+                    if (hi) t_hi = fmaxf(t_hi, v); else t_lo = fmaxf(t_lo, v);
+                }
+            t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 1));
+            t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 2));
+            t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 1));
+            t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 2));
+            const float n_lo = fmaxf(mx[m][0], t_lo), n_hi = fmaxf(mx[m][1], t_hi);
+            float a_lo = 0.f, a_hi = 0.f;
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float v = s[m][n][i];
+                    if (v != -INFINITY) {
+                        if (i >= 2) a_hi += expf(v - n_hi); else a_lo += expf(v - n_lo);
+                    }
+                }
+            a_lo += __shfl_xor_sync(0xffffffffu, a_lo, 1);
+            a_lo += __shfl_xor_sync(0xffffffffu, a_lo, 2);
+            a_hi += __shfl_xor_sync(0xffffffffu, a_hi, 1);
+            a_hi += __shfl_xor_sync(0xffffffffu, a_hi, 2);
+            den[m][0] = (n_lo == -INFINITY ? 0.f : den[m][0] * expf(mx[m][0] - n_lo)) + a_lo;
+            den[m][1] = (n_hi == -INFINITY ? 0.f : den[m][1] * expf(mx[m][1] - n_hi)) + a_hi;
+            mx[m][0] = n_lo;
+            mx[m][1] = n_hi;
+        }
+    }
+    float inv[2][2];
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) inv[m][h] = den[m][h] > 0.f ? (m == 0 ? 1.f : -lambda) / den[m][h] : 0.f;
+
+    // ---- second walk: the signed weights and their product with the values
+    float acc[NT_E][4];
+#pragma unroll
+    for (int n = 0; n < NT_E; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+    const int v_key = ((lane >> 3) & 1) * 8 + (lane & 7), v_col = (lane >> 4) * 8;
+    for (int j0 = 0; j0 <= last_key; j0 += BN) {
+        __syncthreads();
+        load_tile(ks, vs, k_pool, v_pool, table, max_blocks, j0, last_key, g, nkv, page_size, num_pages, true, err);
+        cp_async_wait_all();
+        __syncthreads();
+        if (j0 > warp_last_key) continue;
+        float s[2][4][4];
+        scores(s, qs_warp, ks, lane);
+        unsigned w[4][2];  // [tile of 8 keys][lo, hi] as pairs of bf16
+#pragma unroll
+        for (int n = 0; n < 4; ++n) {
+            float wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int j = j0 + n * 8 + 2 * tq + (i & 1);
+                const int h = i >> 1;
+                float v = 0.f;
+                if (j <= (h ? pos_hi : pos_lo)) {
+                    v = expf(capped(s[0][n][i], scale, cap, inv_cap) - mx[0][h]) * inv[0][h]
+                        + expf(capped(s[1][n][i], scale, cap, inv_cap) - mx[1][h]) * inv[1][h];
+                }
+                wv[i] = v;
+            }
+            w[n][0] = pack_bf16(wv[0], wv[1]);
+            w[n][1] = pack_bf16(wv[2], wv[3]);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {  // 16 keys a step
+            const unsigned a[4] = {w[2 * kk][0], w[2 * kk][1], w[2 * kk + 1][0], w[2 * kk + 1][1]};
+#pragma unroll
+            for (int pr = 0; pr < NT_E / 2; ++pr) {
+                unsigned b0, b1, b2, b3;
+                ldsm_x4_trans(b0, b1, b2, b3, vs + (kk * 16 + v_key) * VS + pr * 16 + v_col);
+                mma_bf16(acc[2 * pr], a, b0, b1);
+                mma_bf16(acc[2 * pr + 1], a, b2, b3);
+            }
+        }
+    }
+
+    // ---- each row divided by its root mean square, times out_scale
+    float ss_lo = 0.f, ss_hi = 0.f;
+#pragma unroll
+    for (int n = 0; n < NT_E; ++n) {
+        ss_lo = fmaf(acc[n][0], acc[n][0], fmaf(acc[n][1], acc[n][1], ss_lo));
+        ss_hi = fmaf(acc[n][2], acc[n][2], fmaf(acc[n][3], acc[n][3], ss_hi));
+    }
+    ss_lo += __shfl_xor_sync(0xffffffffu, ss_lo, 1);
+    ss_lo += __shfl_xor_sync(0xffffffffu, ss_lo, 2);
+    ss_hi += __shfl_xor_sync(0xffffffffu, ss_hi, 1);
+    ss_hi += __shfl_xor_sync(0xffffffffu, ss_hi, 2);
+    const float f_lo = out_scale / sqrtf(ss_lo / (float)E + eps), f_hi = out_scale / sqrtf(ss_hi / (float)E + eps);
+    if (p_lo < n_packed) {
+        bf16* op = out + ((size_t)(row0 + p_lo / R) * nh + g * R + p_lo % R) * E;
+#pragma unroll
+        for (int n = 0; n < NT_E; ++n)
+            *reinterpret_cast<unsigned*>(op + n * 8 + 2 * tq) = pack_bf16(acc[n][0] * f_lo, acc[n][1] * f_lo);
+    }
+    if (p_hi < n_packed) {
+        bf16* op = out + ((size_t)(row0 + p_hi / R) * nh + g * R + p_hi % R) * E;
+#pragma unroll
+        for (int n = 0; n < NT_E; ++n)
+            *reinterpret_cast<unsigned*>(op + n * 8 + 2 * tq) = pack_bf16(acc[n][2] * f_hi, acc[n][3] * f_hi);
+    }
+}
+}  // namespace
+
+IB_EXPORT int ib_attention_diff_mma_d() { return D; }
+IB_EXPORT int ib_attention_diff_mma_e() { return E; }
+
+// q: contiguous bf16 [n_rows, nh, 2 D]; out: contiguous bf16 [n_rows, nh, E]; pools [pages, nkv, page_size, 2 D | E];
+// max_rows_per_entry: an upper bound on the rows of any entry (the grid's width).
+IB_EXPORT int ib_attention_diff_mma(const void* q, const void* k_pool, const void* v_pool, void* out, const int* cu_rows,
+                                    const int* positions, const int* block_tables, int max_blocks, int n_entries,
+                                    int max_rows_per_entry, int nh, int nkv, int page_size, int num_pages, float scale,
+                                    float cap, float lambda, float eps, float out_scale, unsigned* err, void* stream) {
+    if (n_entries <= 0 || max_rows_per_entry <= 0) return IB_OK;
+    if (!q || !k_pool || !v_pool || !out || !cu_rows || !positions || !block_tables || !err) return IB_ERR_BAD_ARG;
+    if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !(eps > 0.f))
+        return IB_ERR_BAD_ARG;
+    if (n_entries > 65535 || nkv > 65535) return IB_ERR_TOO_LARGE;
+    const size_t smem = (size_t)(BM * QS + BN * KS + BN * VS) * sizeof(bf16);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t ce = cudaFuncSetAttribute(attention_diff_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (ce != cudaSuccess) return (int)ce;
+        configured = true;
+    }
+    const int R = nh / nkv;
+    const long long tiles = ((long long)max_rows_per_entry * R + BM - 1) / BM;
+    cudaError_t le = launch_kernel(attention_diff_mma_kernel, dim3((unsigned)tiles, n_entries, nkv), dim3(THREADS), smem,
+                                   (cudaStream_t)stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
+                                   cu_rows, positions, block_tables, max_blocks, nh, nkv, page_size, num_pages, scale, cap,
+                                   lambda, eps, out_scale, err);
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}

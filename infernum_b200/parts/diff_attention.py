@@ -31,7 +31,7 @@ from typing import Dict, Optional
 import torch
 
 from ..errors import ConfigError
-from ..ops import core
+from ..ops import attention_diff, core
 from .base import MIXERS, Mixer, PagedCacheSpec, Runtime, StateSpec, WeightSpec
 from .linear import Linear
 from .rope import rotary_inv_freq, rotary_magnitude
@@ -128,6 +128,9 @@ class DiffAttention(Mixer):
         if self.taps > 1:
             core.conv_state_update(proj, self.taps, cache.state, 0, ctx)
         out = torch.empty((N, self.heads * self.vdim), dtype=x.dtype, device=x.device)
-        core.attention_diff(q, cache.k_pool, cache.v_pool, out, ctx, tables, self.heads, self.scale, self.softcap,
-                            self.lam, self.eps, 1.0 - self.diff, self.rt.err)
+        # bfloat16 with sizes that have a variant: the tensor-core kernel; everything else the plain 32-bit one
+        if not attention_diff.run(q, cache.k_pool, cache.v_pool, out, ctx, tables, self.heads, self.scale, self.softcap,
+                                  self.lam, self.eps, 1.0 - self.diff, self.rt):
+            core.attention_diff(q, cache.k_pool, cache.v_pool, out, ctx, tables, self.heads, self.scale, self.softcap,
+                                self.lam, self.eps, 1.0 - self.diff, self.rt.err)
         return self.o(out)

@@ -520,41 +520,66 @@ def plain_two_maps(q, k, v, scale, cap, lam, eps, out_scale):
     return torch.stack(out, dim=1)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,d,e,page", [(4, 2, 16, 24, 4), (1, 1, 12, 12, 8), (6, 3, 8, 80, 16), (8, 1, 32, 64, 16),
-                                          (2, 2, 64, 130, 32), (3, 1, 10, 300, 16)])
-def test_two_score_maps_over_paged_keys_with_one_key_that_stands_out(dtype, H, G, d, e, page):
-    """Queries at the end of prompts of several lengths, among them rows of one portion; for each
-    query one key - far back, at a page's first or last place, the sequence's first token, the
-    query's own - is scaled so that it alone carries the first map, another one the second."""
-    from infernum_b200.ops import core
+def check_two_maps(dtype, H, G, d, e, page, lens, rows, run, tol):
+    """Queries at the ends of sequences of several lengths (the last ``rows`` of each are one step's
+    entries); for each sequence's last query one key - far back, at a page's first or last place, the
+    sequence's first token, the query's own - is scaled so that it alone carries the first map, another
+    one the second.  ``run(q, k_pool, v_pool, out, step, tables, cap)`` is the kernel under test."""
     g = torch.Generator().manual_seed(H * d + e)
-    lens = [1, 2, page, page + 1, 5 * page - 1, 301, 64]
     scale, cap, lam, eps, out_scale = 0.3, 25.0, 0.37, 1e-5, 0.8
     ks = [torch.randn(t, G, 2, d, generator=g).to(dtype).double() for t in lens]
     vs = [torch.randn(t, G, e, generator=g).to(dtype).double() for t in lens]
     qs = [torch.randn(t, H, 2, d, generator=g).to(dtype).double() for t in lens]
+    places = [0, -1, page - 1, page, None, 3, 0]
     for r, t in enumerate(lens):
-        for m, j in ((0, [0, t - 1, page - 1, page, t // 2, 3, 0][r] % t), (1, (t * 7 // 9) % t)):
+        at = places[r % len(places)]
+        first = (t // 2 if at is None else at) % t
+        for m, j in ((0, first), (1, (t * 7 // 9) % t)):
             ks[r][j, :, m] = (ks[r][j, :, m] * 0 + qs[r][t - 1].mean(0)[m] * 6).to(dtype).double()  # q(t-1) . k(j) large
-    refs = [plain_two_maps(q, k, v, scale, cap, lam, eps, out_scale) for q, k, v in zip(qs, ks, vs)]
     k_pool, v_pool, tables = build_pools([k.reshape(k.shape[0], G, 2 * d) for k in ks], vs, page, dtype, seed=e)
-    # the step: the last min(t, 5) rows of every request
-    rows = [min(t, 5) for t in lens]
     step = Step(rows, list(range(len(lens))), [t - n for t, n in zip(lens, rows)])
     q = torch.cat([qq[t - n:] for qq, t, n in zip(qs, lens, rows)]).reshape(-1, H * 2 * d).to(dtype).to(DEV)
-    out = torch.empty(q.shape[0], H * e, dtype=dtype, device=DEV)
+    for use_cap in (cap, None):
+        refs = [plain_two_maps(qq, k, v, scale, use_cap, lam, eps, out_scale) for qq, k, v in zip(qs, ks, vs)]
+        ref = torch.cat([rf[t - n:] for rf, t, n in zip(refs, lens, rows)]).reshape(-1, H * e)
+        out = torch.full((q.shape[0], H * e), float("nan"), dtype=dtype, device=DEV)
+        run(q, k_pool, v_pool, out, step, tables, (scale, use_cap or 0.0, lam, eps, out_scale))
+        assert torch.isfinite(out).all()
+        assert rel_err(out, ref) < tol, f"cap {use_cap}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,d,e,page", [(4, 2, 16, 24, 4), (1, 1, 12, 12, 8), (6, 3, 8, 80, 16), (8, 1, 32, 64, 16),
+                                          (2, 2, 64, 130, 32), (3, 1, 10, 300, 16)])
+def test_two_score_maps_over_paged_keys_with_one_key_that_stands_out(dtype, H, G, d, e, page):
+    from infernum_b200.ops import core
     rt = runtime(dtype)
-    core.attention_diff(q, k_pool, v_pool, out, step, tables, H, scale, cap, lam, eps, out_scale, rt.err)
+
+    def run(q, k_pool, v_pool, out, step, tables, consts):
+        core.attention_diff(q, k_pool, v_pool, out, step, tables, H, *consts, rt.err)
+
+    lens = [1, 2, page, page + 1, 5 * page - 1, 301, 64]
+    check_two_maps(dtype, H, G, d, e, page, lens, [min(t, 5) for t in lens], run, 2e-5 if dtype == torch.float32 else 3e-2)
     assert int(rt.err.item()) == 0
-    ref = torch.cat([rf[t - n:] for rf, t, n in zip(refs, lens, rows)]).reshape(-1, H * e)
-    assert torch.isfinite(out).all()
-    assert rel_err(out, ref) < (2e-5 if dtype == torch.float32 else 3e-2)
-    # no cap on the scores
-    refs = [plain_two_maps(qq, k, v, scale, None, lam, eps, out_scale) for qq, k, v in zip(qs, ks, vs)]
-    core.attention_diff(q, k_pool, v_pool, out, step, tables, H, scale, 0.0, lam, eps, out_scale, rt.err)
-    ref = torch.cat([rf[t - n:] for rf, t, n in zip(refs, lens, rows)]).reshape(-1, H * e)
-    assert rel_err(out, ref) < (2e-5 if dtype == torch.float32 else 3e-2)
+
+
+@pytest.mark.parametrize("H,G,d,e,page", [(4, 2, 16, 32, 4), (1, 1, 16, 16, 8), (6, 3, 16, 80, 16), (8, 1, 32, 64, 16),
+                                          (8, 2, 128, 256, 16), (3, 1, 64, 128, 32), (16, 2, 48, 96, 16)])
+def test_two_score_maps_on_the_tensor_cores(H, G, d, e, page):
+    """The same through the tensor-core kernel: whole prompts that fill several row tiles, portions
+    behind cached keys, single decoded rows far into a sequence, an entry without rows in the middle."""
+    from infernum_b200.ops import attention_diff
+    rt = runtime(torch.bfloat16)
+    assert attention_diff.supported(d, e)
+
+    def run(q, k_pool, v_pool, out, step, tables, consts):
+        step.max_rows_per_entry = max(rows)
+        assert attention_diff.run(q, k_pool, v_pool, out, step, tables, H, *consts, rt)
+
+    lens = [1, 2, page, page + 1, 150, 301, 64, 97, 33]
+    rows = [1, 2, 1, page + 1, 150, 1, 40, 0, 33]
+    check_two_maps(torch.bfloat16, H, G, d, e, page, lens, rows, run, 3e-2)
+    assert int(rt.err.item()) == 0
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
