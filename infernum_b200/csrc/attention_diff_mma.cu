@@ -18,6 +18,12 @@
 // absolute multiples of 32 whatever the step's cut, through the block table, by cp.async into
 // padded shared memory; rows beyond the last key any row of the CTA sees are zero-filled, so
 // what an earlier user left in a page never meets a zero weight.
+//
+// Steps of few rows (decoded tokens) would leave one CTA per entry and key/value head walking
+// all keys alone.  For those the keys are cut in slices over several CTAs and the two walks
+// become two launches: the first writes every slice's maxima and denominators, the second
+// merges them, walks its slice again and writes its share of w V in 32-bit; a third kernel
+// adds the shares in slice order and norms.
 #include "common.cuh"
 
 using namespace ib;
@@ -132,19 +138,26 @@ __device__ __forceinline__ float capped(float s, float scale, float cap, float i
     return cap > 0.f ? cap * tanhf(s * inv_cap) : s;
 }
 
+// MODE 0: both walks over all keys, the normed result to `out`.  MODE 1: the first walk over the
+// CTA's slice of the keys; maxima and denominators to `stats` [splits][rows][heads][4].  MODE 2:
+// the slices' maxima and denominators merged, the second walk over the CTA's slice, its share
+// of w V to `part` [splits][rows][heads][E] (32-bit, not normed).
+template <int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                           bf16* __restrict__ out, const int* __restrict__ cu_rows, const int* __restrict__ positions,
                           const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int page_size,
                           int num_pages, float scale, float cap, float lambda, float eps, float out_scale,
-                          unsigned* __restrict__ err) {
+                          unsigned* __restrict__ err, int splits, int slice_len, int n_total_rows,
+                          float* __restrict__ stats, float* __restrict__ part) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* qs = reinterpret_cast<bf16*>(smem_raw);
     bf16* ks = qs + BM * QS;
     bf16* vs = ks + BN * KS;
-    const int en = blockIdx.y, g = blockIdx.z;
+    const int en = blockIdx.y, g = MODE == 0 ? blockIdx.z : blockIdx.z / splits;
+    const int sp = MODE == 0 ? 0 : blockIdx.z % splits;
     const int R = nh / nkv;
     const int row0 = cu_rows[en], n_rows = cu_rows[en + 1] - row0;
     const int n_packed = n_rows * R;
@@ -155,7 +168,9 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
     const int* table = block_tables + (size_t)en * max_blocks;
     const int pos0 = positions[row0];  // an entry's rows are consecutive positions
     const int packed_here = min(BM, n_packed - tile0);
-    const int last_key = pos0 + (tile0 + packed_here - 1) / R;  // what the CTA's last row sees
+    const int last_seen = pos0 + (tile0 + packed_here - 1) / R;  // what the CTA's last row sees
+    const int first_key = MODE == 0 ? 0 : sp * slice_len;         // (slices are multiples of a tile)
+    const int last_key = MODE == 0 ? last_seen : min(last_seen, first_key + slice_len - 1);
 
     // queries: packed row p = (row p / R, head g R + p % R), both maps side by side
     {
@@ -178,7 +193,7 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
 
     // ---- first walk: maxima and denominators of both maps
     float mx[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, den[2][2] = {{0.f, 0.f}, {0.f, 0.f}};  // [map][lo, hi]
-    for (int j0 = 0; j0 <= last_key; j0 += BN) {
+    for (int j0 = first_key; MODE != 2 && j0 <= last_key; j0 += BN) {
         __syncthreads();  // the tile before is done with
         load_tile(ks, vs, k_pool, v_pool, table, max_blocks, j0, last_key, g, nkv, page_size, num_pages, false, err);
         cp_async_wait_all();
@@ -224,6 +239,44 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
             mx[m][1] = n_hi;
         }
     }
+    if (MODE == 1) {
+        cp_async_wait_all();  // (the queries, when the slice held no key)
+        if (tq == 0) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int p = h ? p_hi : p_lo;
+                if (p < n_packed) {
+                    float* dst = stats + (((size_t)sp * n_total_rows + row0 + p / R) * nh + g * R + p % R) * 4;
+                    dst[0] = mx[0][h];
+                    dst[1] = den[0][h];
+                    dst[2] = mx[1][h];
+                    dst[3] = den[1][h];
+                }
+            }
+        }
+        return;
+    }
+    if (MODE == 2) {
+        // the slices' maxima and denominators merged in slice order
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int p = h ? p_hi : p_lo;
+            if (p >= n_packed) continue;
+            const float* src = stats + (((size_t)(row0 + p / R)) * nh + g * R + p % R) * 4;
+            const size_t step = (size_t)n_total_rows * nh * 4;
+            for (int m = 0; m < 2; ++m) {
+                float best = -INFINITY;
+                for (int k = 0; k < splits; ++k) best = fmaxf(best, src[k * step + 2 * m]);
+                float sum = 0.f;
+                for (int k = 0; k < splits; ++k) {
+                    const float mk = src[k * step + 2 * m];
+                    if (mk != -INFINITY) sum += src[k * step + 2 * m + 1] * expf(mk - best);
+                }
+                mx[m][h] = best;
+                den[m][h] = sum;
+            }
+        }
+    }
     float inv[2][2];
 #pragma unroll
     for (int m = 0; m < 2; ++m)
@@ -237,7 +290,8 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
     const int v_key = ((lane >> 3) & 1) * 8 + (lane & 7), v_col = (lane >> 4) * 8;
-    for (int j0 = 0; j0 <= last_key; j0 += BN) {
+    if (MODE == 2 && first_key > last_key) cp_async_wait_all();  // (the queries; nothing else follows)
+    for (int j0 = first_key; j0 <= last_key; j0 += BN) {
         __syncthreads();
         load_tile(ks, vs, k_pool, v_pool, table, max_blocks, j0, last_key, g, nkv, page_size, num_pages, true, err);
         cp_async_wait_all();
@@ -276,6 +330,18 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
         }
     }
 
+    if (MODE == 2) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int p = h ? p_hi : p_lo;
+            if (p >= n_packed) continue;
+            float* dst = part + (((size_t)sp * n_total_rows + row0 + p / R) * nh + g * R + p % R) * E;
+#pragma unroll
+            for (int n = 0; n < NT_E; ++n)
+                *reinterpret_cast<float2*>(dst + n * 8 + 2 * tq) = make_float2(acc[n][2 * h], acc[n][2 * h + 1]);
+        }
+        return;
+    }
     // ---- each row divided by its root mean square, times out_scale
     float ss_lo = 0.f, ss_hi = 0.f;
 #pragma unroll
@@ -301,17 +367,51 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
             *reinterpret_cast<unsigned*>(op + n * 8 + 2 * tq) = pack_bf16(acc[n][2] * f_hi, acc[n][3] * f_hi);
     }
 }
+// The slices' shares added in slice order, each (row, head) divided by its root mean square: a warp each.
+__global__ void attention_diff_merge_kernel(const float* __restrict__ part, bf16* __restrict__ out, int splits,
+                                            int n_rows, int nh, float eps, float out_scale) {
+    pdl_trigger();
+    pdl_wait();
+    const int item = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (item >= n_rows * nh) return;
+    constexpr int PER = (E + 31) / 32;
+    float v[PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = lane + 32 * i;
+        float a = 0.f;
+        if (c < E)
+            for (int k = 0; k < splits; ++k) a += part[((size_t)k * n_rows * nh + item) * E + c];
+        v[i] = a;
+        ss = fmaf(a, a, ss);
+    }
+    ss = warp_sum(ss);
+    const float f = out_scale / sqrtf(ss / (float)E + eps);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = lane + 32 * i;
+        if (c < E) out[(size_t)item * E + c] = __float2bfloat16_rn(v[i] * f);
+    }
+}
 }  // namespace
 
 IB_EXPORT int ib_attention_diff_mma_d() { return D; }
 IB_EXPORT int ib_attention_diff_mma_e() { return E; }
 
 // q: contiguous bf16 [n_rows, nh, 2 D]; out: contiguous bf16 [n_rows, nh, E]; pools [pages, nkv, page_size, 2 D | E];
-// max_rows_per_entry: an upper bound on the rows of any entry (the grid's width).
+// max_rows_per_entry: an upper bound on the rows of any entry (the grid's width).  splits > 1: the keys in
+// slices of `slice_len` (a multiple of 32; splits * slice_len covers every key any row sees) over that many
+// CTAs, through `scratch` (ib_attention_diff_mma_scratch_bytes); n_rows: all rows of the step.
+IB_EXPORT long long ib_attention_diff_mma_scratch_bytes(int n_rows, int nh, int splits) {
+    return (long long)splits * n_rows * nh * (4 + E) * (long long)sizeof(float);
+}
+
 IB_EXPORT int ib_attention_diff_mma(const void* q, const void* k_pool, const void* v_pool, void* out, const int* cu_rows,
                                     const int* positions, const int* block_tables, int max_blocks, int n_entries,
                                     int max_rows_per_entry, int nh, int nkv, int page_size, int num_pages, float scale,
-                                    float cap, float lambda, float eps, float out_scale, unsigned* err, void* stream) {
+                                    float cap, float lambda, float eps, float out_scale, unsigned* err, int n_rows,
+                                    int splits, int slice_len, void* scratch, long long scratch_bytes, void* stream) {
     if (n_entries <= 0 || max_rows_per_entry <= 0) return IB_OK;
     if (!q || !k_pool || !v_pool || !out || !cu_rows || !positions || !block_tables || !err) return IB_ERR_BAD_ARG;
     if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !(eps > 0.f))
@@ -320,16 +420,43 @@ IB_EXPORT int ib_attention_diff_mma(const void* q, const void* k_pool, const voi
     const size_t smem = (size_t)(BM * QS + BN * KS + BN * VS) * sizeof(bf16);
     static bool configured = false;
     if (!configured) {
-        cudaError_t ce = cudaFuncSetAttribute(attention_diff_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t ce = cudaFuncSetAttribute(attention_diff_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (ce == cudaSuccess)
+            ce = cudaFuncSetAttribute(attention_diff_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (ce == cudaSuccess)
+            ce = cudaFuncSetAttribute(attention_diff_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (ce != cudaSuccess) return (int)ce;
         configured = true;
     }
     const int R = nh / nkv;
     const long long tiles = ((long long)max_rows_per_entry * R + BM - 1) / BM;
-    cudaError_t le = launch_kernel(attention_diff_mma_kernel, dim3((unsigned)tiles, n_entries, nkv), dim3(THREADS), smem,
-                                   (cudaStream_t)stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out,
-                                   cu_rows, positions, block_tables, max_blocks, nh, nkv, page_size, num_pages, scale, cap,
-                                   lambda, eps, out_scale, err);
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t le;
+    if (splits <= 1) {
+        le = launch_kernel(attention_diff_mma_kernel<0>, dim3((unsigned)tiles, n_entries, nkv), dim3(THREADS), smem, s,
+                           (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, cu_rows, positions,
+                           block_tables, max_blocks, nh, nkv, page_size, num_pages, scale, cap, lambda, eps, out_scale, err,
+                           1, 0, n_rows, (float*)nullptr, (float*)nullptr);
+        if (le != cudaSuccess) return (int)le;
+        IB_LAUNCH_CHECK();
+        return IB_OK;
+    }
+    if (!scratch || slice_len <= 0 || slice_len % BN || n_rows <= 0 || (long long)nkv * splits > 65535) return IB_ERR_BAD_ARG;
+    if (scratch_bytes < ib_attention_diff_mma_scratch_bytes(n_rows, nh, splits)) return IB_ERR_BAD_ARG;
+    float* stats = (float*)scratch;
+    float* part = stats + (size_t)splits * n_rows * nh * 4;
+    const dim3 grid((unsigned)tiles, n_entries, nkv * splits);
+    le = launch_kernel(attention_diff_mma_kernel<1>, grid, dim3(THREADS), smem, s, (const bf16*)q, (const bf16*)k_pool,
+                       (const bf16*)v_pool, (bf16*)out, cu_rows, positions, block_tables, max_blocks, nh, nkv, page_size,
+                       num_pages, scale, cap, lambda, eps, out_scale, err, splits, slice_len, n_rows, stats, part);
+    if (le != cudaSuccess) return (int)le;
+    le = launch_kernel(attention_diff_mma_kernel<2>, grid, dim3(THREADS), smem, s, (const bf16*)q, (const bf16*)k_pool,
+                       (const bf16*)v_pool, (bf16*)out, cu_rows, positions, block_tables, max_blocks, nh, nkv, page_size,
+                       num_pages, scale, cap, lambda, eps, out_scale, err, splits, slice_len, n_rows, stats, part);
+    if (le != cudaSuccess) return (int)le;
+    const long long warps = (long long)n_rows * nh;
+    le = launch_kernel(attention_diff_merge_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, s, (const float*)part,
+                       (bf16*)out, splits, n_rows, nh, eps, out_scale);
     if (le != cudaSuccess) return (int)le;
     IB_LAUNCH_CHECK();
     return IB_OK;

@@ -232,11 +232,13 @@ IB_EXPORT int ib_moe_route_scored(const float* logits, int ld, const float* bias
 // with that weight.  Written: ids / weights [N, top]; the dense row gate[N, E] for the
 // experts that exist; extra[N, 2] = (the sum of the weights that fell on the outputs
 // without an expert, sigmoid(z[E_all]) when the logits carry one more column - the gate of
-// an expert that every token uses - else 1).
+// an expert that every token uses - else 1).  With gate_cols > E the dense row is that wide and its
+// columns from E on hold extra[n, 1]: the expert that every token uses, run as further columns of the
+// experts' products.
 __global__ void moe_route_softmax_all_kernel(const float* __restrict__ logits, int ld,
                                              const float* __restrict__ correction, int E_all, int E, int top,
                                              int with_gate, int* __restrict__ ids, float* __restrict__ weights,
-                                             float* __restrict__ gate, float* __restrict__ extra) {
+                                             float* __restrict__ gate, float* __restrict__ extra, int gate_cols) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float sm[];
@@ -259,7 +261,7 @@ __global__ void moe_route_softmax_all_kernel(const float* __restrict__ logits, i
         const float v = s[e] / denom;
         s[e] = v;
         c[e] = v + (correction ? correction[e] : 0.f);
-        if (gate && e < E) gate[(size_t)row * E + e] = 0.f;
+        if (gate && e < E) gate[(size_t)row * gate_cols + e] = 0.f;
     }
     __syncwarp();
     float sum = 0.f;
@@ -292,29 +294,32 @@ __global__ void moe_route_softmax_all_kernel(const float* __restrict__ logits, i
             const float w = s[at] * inv;
             weights[(size_t)row * top + k] = w;
             if (at < E) {
-                if (gate) gate[(size_t)row * E + at] = w;
+                if (gate) gate[(size_t)row * gate_cols + at] = w;
             } else {
                 passed += w;
             }
         }
+        const float every = with_gate ? 1.f / (1.f + expf(-src[E_all])) : 1.f;
         if (extra) {
             extra[(size_t)row * 2] = passed;
-            extra[(size_t)row * 2 + 1] = with_gate ? 1.f / (1.f + expf(-src[E_all])) : 1.f;
+            extra[(size_t)row * 2 + 1] = every;
         }
+        if (gate)
+            for (int e = E; e < gate_cols; ++e) gate[(size_t)row * gate_cols + e] = every;
     }
 }
 
 IB_EXPORT int ib_moe_route_softmax_all(const float* logits, int ld, const float* correction, int E_all, int E, int top,
                                        int with_gate, int* ids, float* weights, float* gate, float* extra,
-                                       int n_rows, void* stream) {
+                                       int gate_cols, int n_rows, void* stream) {
     if (n_rows <= 0) return IB_OK;
     if (!logits || !ids || !weights || E_all <= 0 || E < 0 || E > E_all || top <= 0 || top > E_all ||
-        ld < E_all + (with_gate ? 1 : 0))
+        ld < E_all + (with_gate ? 1 : 0) || (gate && gate_cols < E))
         return IB_ERR_BAD_ARG;
     const size_t smem = (size_t)E_all * 2 * sizeof(float);
     if (smem > 48 * 1024) return IB_ERR_TOO_LARGE;
     cudaError_t le = launch_kernel(moe_route_softmax_all_kernel, dim3(n_rows), dim3(32), smem, (cudaStream_t)stream,
-                                   logits, ld, correction, E_all, E, top, with_gate, ids, weights, gate, extra);
+                                   logits, ld, correction, E_all, E, top, with_gate, ids, weights, gate, extra, gate_cols);
     if (le != cudaSuccess) return (int)le;
     IB_LAUNCH_CHECK();
     return IB_OK;

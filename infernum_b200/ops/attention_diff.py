@@ -4,6 +4,11 @@ one compiled module per (map size, value size), built when a model first needs i
 ``run`` returns False when the sizes have no variant (bfloat16; map and value
 sizes multiples of 16, at most 256) or ``rt.options["attention"] == "plain"``;
 the caller then takes the plain 32-bit kernel (``core.attention_diff``).
+
+A step whose entries all have few rows (decoded tokens) would run one CTA per
+entry and key/value head; ``choose_splits`` then cuts the keys in slices over
+several CTAs (two launches and a merge).  The plan and the scratch buffer are
+worked out once per step and kept in ``ctx.scratch``.
 """
 
 from __future__ import annotations
@@ -31,12 +36,34 @@ def lib_for(dim: int, vdim: int) -> ctypes.CDLL:
         lib = load_module(f"attn_diff_d{dim}_e{vdim}", ["attention_diff_mma.cu"], [f"-DDIFF_D={dim}", f"-DDIFF_E={vdim}"])
         lib.ib_attention_diff_mma.argtypes = [
             _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
-            _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_float, _c_float, _c_void_p, _c_void_p]
+            _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_float, _c_float, _c_void_p, _c_int, _c_int, _c_int,
+            _c_void_p, ctypes.c_longlong, _c_void_p]
         lib.ib_attention_diff_mma.restype = _c_int
+        lib.ib_attention_diff_mma_scratch_bytes.argtypes = [_c_int, _c_int, _c_int]
+        lib.ib_attention_diff_mma_scratch_bytes.restype = ctypes.c_longlong
         if lib.ib_attention_diff_mma_d() != dim or lib.ib_attention_diff_mma_e() != vdim:
             raise KernelError(f"differential attention module for ({dim}, {vdim}) was built for other sizes")
         _libs[(dim, vdim)] = lib
     return lib
+
+
+SM_COUNT_FALLBACK = 148
+ROW_TILE, KEY_TILE, MAX_SPLITS = 64, 32, 64
+
+
+def choose_splits(max_rows_per_entry: int, n_entries: int, group: int, kv_heads: int, max_kv_len: int,
+                  sm_count: int) -> Tuple[int, int]:
+    """(slices of the keys, keys per slice).  One slice unless every entry fits one row tile, the CTAs
+    leave SMs idle and there are keys enough for slices of at least two tiles; then as many slices as
+    fill the SMs about four times (a CTA waits for its keys most of the time)."""
+    ctas = max(1, n_entries * kv_heads)
+    if max_rows_per_entry * group > ROW_TILE or ctas >= 2 * sm_count or max_kv_len < 4 * KEY_TILE:
+        return 1, 0
+    want = min(-(-4 * sm_count // ctas), max_kv_len // (2 * KEY_TILE), MAX_SPLITS, 65535 // max(kv_heads, 1))
+    if want < 2:
+        return 1, 0
+    slice_len = -(-(-(-max_kv_len // want)) // KEY_TILE) * KEY_TILE
+    return -(-max_kv_len // slice_len), slice_len
 
 
 def run(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, ctx, tables: torch.Tensor,
@@ -54,11 +81,30 @@ def run(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.
         raise KernelError("attention_diff_mma: q [N, heads * 2 dim], out [N, heads * vdim] and the pools do not fit")
     core.require_cuda(q, k_pool, v_pool, out, tables)
     lib = lib_for(dim, vdim)
+    key = ("diff_plan", n_heads, nkv, dim, vdim)
+    plan = ctx.scratch.get(key) if hasattr(ctx, "scratch") else None
+    if plan is None:
+        forced = rt.options.get("diff_splits")
+        plan = tuple(forced) if forced else choose_splits(
+            ctx.max_rows_per_entry, ctx.n_entries, n_heads // nkv, nkv, getattr(ctx, "max_kv_len", 0),
+            rt.options.get("sm_count") or SM_COUNT_FALLBACK)
+        if hasattr(ctx, "scratch"):
+            ctx.scratch[key] = plan
+    splits, slice_len = plan
+    scratch_ptr, scratch_bytes = None, 0
+    if splits > 1:
+        need = lib.ib_attention_diff_mma_scratch_bytes(N, n_heads, splits)
+        buf = ctx.scratch.get("diff_split") if hasattr(ctx, "scratch") else None
+        if buf is None or buf.numel() * 4 < need:
+            buf = torch.empty((need + 3) // 4, dtype=torch.float32, device=q.device)
+            if hasattr(ctx, "scratch"):
+                ctx.scratch["diff_split"] = buf
+        scratch_ptr, scratch_bytes = buf.data_ptr(), buf.numel() * 4
     code = lib.ib_attention_diff_mma(
         q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), ctx.cu_rows.data_ptr(),
         ctx.positions.data_ptr(), tables.data_ptr(), tables.shape[1], ctx.n_entries, ctx.max_rows_per_entry, n_heads, nkv,
         page_size, num_pages, float(scale), float(softcap or 0.0), float(lam), float(eps), float(out_scale),
-        rt.err.data_ptr(), core.stream_ptr(q))
+        rt.err.data_ptr(), N, splits, slice_len, scratch_ptr, scratch_bytes, core.stream_ptr(q))
     core.check(code, "attention_diff_mma")
     core.profile_mark("attention_diff_mma")
     return True

@@ -157,7 +157,7 @@ def core_lib() -> ctypes.CDLL:
         lib.ib_latent_prepare_ex.argtypes = lib.ib_latent_prepare.argtypes[:22] + [_c_int, _c_float, _c_void_p, _c_void_p]
         lib.ib_latent_q_rotate_ex.argtypes = lib.ib_latent_q_rotate.argtypes[:14] + [_c_int, _c_float, _c_void_p]
         lib.ib_moe_route_softmax_all.argtypes = [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p,
-                                                 _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p]
+                                                 _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p]
         lib.ib_moe_combine.argtypes = [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                                        _c_int, _c_void_p]
         lib.ib_gated_norm_add.argtypes = [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_float,
@@ -1301,7 +1301,7 @@ def moe_route_softmax_all(logits: torch.Tensor, correction: Optional[torch.Tenso
     (lowest index among equals), their weights are ``s`` over the chosen ones' sum (+ 1e-20).  Outputs
     from ``experts`` on have no expert: their weight is summed into ``extra[:, 0]``.  ``gate`` [N, experts]
     gets the dense weights of the experts that exist.  When ``logits`` has one more column, ``extra[:, 1]``
-    is its sigmoid, else 1."""
+    is its sigmoid, else 1; a ``gate`` wider than ``experts`` gets that number in its further columns."""
     require_cuda(logits, correction, ids, weights, gate, extra)
     _int32(ids, "ids")
     N, cols = logits.shape
@@ -1310,13 +1310,15 @@ def moe_route_softmax_all(logits: torch.Tensor, correction: Optional[torch.Tenso
             or weights.dtype != torch.float32 or not weights.is_contiguous():
         raise KernelError("moe_route_softmax_all: logits float32 [N, outputs (+ 1)], ids int32 and weights float32 [N, top]")
     _f32_vec(correction, outputs, "moe_route_softmax_all: correction")
-    if gate is not None and (gate.dtype != torch.float32 or gate.shape != (N, experts) or not gate.is_contiguous()):
-        raise KernelError("moe_route_softmax_all: gate must be contiguous float32 [N, experts]")
+    if gate is not None and (gate.dtype != torch.float32 or gate.dim() != 2 or gate.shape[0] != N
+                             or gate.shape[1] < experts or not gate.is_contiguous()):
+        raise KernelError("moe_route_softmax_all: gate must be contiguous float32 [N, >= experts]")
     if extra is not None and (extra.dtype != torch.float32 or extra.shape != (N, 2) or not extra.is_contiguous()):
         raise KernelError("moe_route_softmax_all: extra must be contiguous float32 [N, 2]")
     check(core_lib().ib_moe_route_softmax_all(logits.data_ptr(), logits.stride(0), _ptr(correction), int(outputs),
                                               int(experts), int(top), 1 if cols == outputs + 1 else 0, ids.data_ptr(),
-                                              weights.data_ptr(), _ptr(gate), _ptr(extra), N, stream_ptr(logits)),
+                                              weights.data_ptr(), _ptr(gate), _ptr(extra),
+                                              gate.shape[1] if gate is not None else int(experts), N, stream_ptr(logits)),
           "moe_route_softmax_all")
 
 

@@ -33,7 +33,9 @@ without the correction over the chosen ones' sum (+ 1e-20); the last
 weight times the token's input.  ``shared`` ({"size", "prefix", "gate"}): one more
 gated feed-forward that every token uses, added times ``sigmoid(w_gate . x)``
 (one number per token; ``gate`` names the [1, hidden] tensor behind the shared
-expert's prefix, None: no gate).
+expert's prefix, None: no gate).  When its width is a multiple of an expert's, it
+runs as further columns of the experts' two products, its gate in the dense row
+of weights; otherwise as a feed-forward of its own.
 """
 
 from __future__ import annotations
@@ -130,9 +132,19 @@ class MixtureOfExperts(FeedForward):
         downs = [weights[self._name(e, "down")] for e in range(E)]
         if len({t.dtype for t in gates + ups + downs}) != 1:
             raise ConfigError(f"{self.prefix}: the experts are stored in different dtypes")
-        # one gated feed-forward of width E * ff: expert e owns outputs [e ff, (e + 1) ff)
+        # one gated feed-forward of width E * ff: expert e owns outputs [e ff, (e + 1) ff); an expert that
+        # every token uses, of k times an expert's width, is k more runs of columns behind them
+        self.shared_runs = 0
+        if self.shared and self.shared["size"] % f == 0:
+            sp = self.shared["prefix"]
+            extra = [weights[sp + "gate"], weights[sp + "up"], weights[sp + "down"]]
+            if {t.dtype for t in extra} == {gates[0].dtype}:
+                self.shared_runs = self.shared["size"] // f
+                gates.append(extra[0])
+                ups.append(extra[1])
+                downs.append(extra[2])
         gate, up = torch.cat(gates, dim=0), torch.cat(ups, dim=0)
-        I = E * f
+        I = (E + self.shared_runs) * f
         self.block = None
         if I % 64 == 0:
             fused = torch.stack([gate.view(I // 64, 64, h), up.view(I // 64, 64, h)], dim=1).reshape(2 * I, h)
@@ -150,10 +162,11 @@ class MixtureOfExperts(FeedForward):
             from .mlp import SwiGLU
 
             sp = self.shared["prefix"]
-            self.shared_ffn = SwiGLU({"hidden_size": h, "intermediate_size": self.shared["size"], "prefix": sp,
-                                      "names": {"gate": "gate", "up": "up", "down": "down"},
-                                      "activation": self.activation}, self.rt)
-            self.shared_ffn.bind(weights)
+            if not self.shared_runs:
+                self.shared_ffn = SwiGLU({"hidden_size": h, "intermediate_size": self.shared["size"], "prefix": sp,
+                                          "names": {"gate": "gate", "up": "up", "down": "down"},
+                                          "activation": self.activation}, self.rt)
+                self.shared_ffn.bind(weights)
             if self.shared["gate"]:
                 # the gate's logit is one more row of the router's product
                 self.router = torch.cat([self.router, weights[sp + self.shared["gate"]].to(self.router.dtype)],
@@ -170,7 +183,7 @@ class MixtureOfExperts(FeedForward):
         core.router_logits(x, self.router, logits)  # 32-bit multiply-adds, a fixed order per row
         ids = torch.empty((n, self.top), dtype=torch.int32, device=dev)
         wts = torch.empty((n, self.top), dtype=torch.float32, device=dev)
-        gate = torch.empty((n, self.experts), dtype=torch.float32, device=dev)
+        gate = torch.empty((n, self.experts + getattr(self, "shared_runs", 0)), dtype=torch.float32, device=dev)
         if self.scoring == "softmax_all":
             self._extra = torch.empty((n, 2), dtype=torch.float32, device=dev)
             core.moe_route_softmax_all(logits, self.correction, self.experts + self.identity, self.experts, self.top,
@@ -184,7 +197,7 @@ class MixtureOfExperts(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx=None) -> torch.Tensor:
         _ids, _wts, gate = self.route(x)
-        act = torch.empty((x.shape[0], self.experts * self.expert_size), dtype=x.dtype, device=x.device)
+        act = torch.empty((x.shape[0], gate.shape[1] * self.expert_size), dtype=x.dtype, device=x.device)
         fused = False
         if self.block == 64 and x.dtype == torch.bfloat16 and self.gate_up.weight.dtype == torch.bfloat16:
             from ..ops import gemm_tc
@@ -197,7 +210,7 @@ class MixtureOfExperts(FeedForward):
                            cols_per_scale=self.expert_size)
         routed = self.down(act)
         if self.scoring != "softmax_all" or not (self.identity or self.shared_ffn is not None):
-            return routed
+            return routed  # (an expert for every token that ran as columns of the products is in there)
         # the input handed on by the outputs without an expert, and the expert that every token uses
         shared = self.shared_ffn.forward(x, ctx) if self.shared_ffn is not None else None
         out = torch.empty_like(routed)

@@ -580,6 +580,24 @@ def test_two_score_maps_on_the_tensor_cores(H, G, d, e, page):
     rows = [1, 2, 1, page + 1, 150, 1, 40, 0, 33]
     check_two_maps(torch.bfloat16, H, G, d, e, page, lens, rows, run, 3e-2)
     assert int(rt.err.item()) == 0
+    # steps of few rows with the keys cut in slices over CTAs: slices that end inside a sequence, slices
+    # behind a sequence's last key, a slice of one tile, as many slices as there are tiles
+    lens = [1, 2, 33, 64, 301, 300, 97, 129]
+    rows = [1, 2, 1, 3, 1, 2, 0, 1]
+    for plan in ((2, 160), (5, 64), (10, 32), (3, 128)):
+        rt.options["diff_splits"] = plan
+        check_two_maps(torch.bfloat16, H, G, d, e, page, lens, rows, run, 3e-2)
+    assert int(rt.err.item()) == 0
+
+
+def test_slices_of_the_keys_are_chosen_for_steps_of_few_rows():
+    from infernum_b200.ops.attention_diff import choose_splits
+    assert choose_splits(512, 1, 4, 2, 2048, 148) == (1, 0)          # a prompt: row tiles fill the machine
+    assert choose_splits(1, 128, 4, 4, 1024, 148) == (1, 0)          # many decoded rows: CTAs enough
+    assert choose_splits(1, 8, 4, 2, 100, 148) == (1, 0)             # few keys
+    for entries, kv_heads, keys in ((1, 2, 1024), (8, 2, 1024), (1, 1, 9000), (3, 4, 300)):
+        splits, slice_len = choose_splits(1, entries, 4, kv_heads, keys, 148)
+        assert splits > 1 and slice_len % 32 == 0 and splits * slice_len >= keys > (splits - 1) * slice_len
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -649,6 +667,10 @@ def test_routing_by_a_softmax_over_all_outputs(E, I, top):
     assert rel_err(gate, dense[:, :E]) < 1e-5
     assert (extra[:, 0].cpu().double() - dense[:, E:].sum(1)).abs().max() < 1e-5
     assert rel_err(extra[:, 1], torch.sigmoid(z[:, A].double())) < 1e-5
+    # a dense row wider than the experts carries the extra column's gate in its further columns
+    wide = torch.empty(N, E + 3, dtype=torch.float32, device=DEV)
+    core.moe_route_softmax_all(z.to(DEV), corr_rows.to(DEV), A, E, top, ids, wts, wide, extra)
+    assert torch.equal(wide[:, :E], gate) and torch.equal(wide[:, E:], extra[:, 1:2].expand(N, 3))
     # without the extra column there is no gate to take; without a correction equal scores meet
     core.moe_route_softmax_all(z[:, :A].contiguous().to(DEV), None, A, E, top, ids, wts, gate, extra)
     assert float((extra[:, 1] - 1).abs().max()) == 0.0
