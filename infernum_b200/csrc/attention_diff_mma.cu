@@ -16,8 +16,9 @@
 // A CTA (four warps) takes 64 packed rows - (query row, head of the group) pairs that share a
 // key/value head - of one entry; a warp 16 of them.  Keys come in tiles of 32 that start at
 // absolute multiples of 32 whatever the step's cut, through the block table, by cp.async into
-// padded shared memory; rows beyond the last key any row of the CTA sees are zero-filled, so
-// what an earlier user left in a page never meets a zero weight.
+// padded shared memory, two stages: a tile is fetched while the one before it is computed on.
+// Rows beyond the last key any row of the CTA sees are zero-filled, so what an earlier user
+// left in a page never meets a zero weight.
 //
 // Steps of few rows (decoded tokens) would leave one CTA per entry and key/value head walking
 // all keys alone.  For those the keys are cut in slices over several CTAs and the two walks
@@ -66,6 +67,9 @@ __device__ __forceinline__ void cp_async16(bf16* smem, const bf16* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(a), "l"(gmem));
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+// all but the newest group of copies have landed
+__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
 
 // One tile of keys (and, with_v, values) into shared memory; rows of keys beyond `last_key` are zeros.
 __device__ __forceinline__ void load_tile(bf16* ks, bf16* vs, const bf16* __restrict__ k_pool,
@@ -154,8 +158,8 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* qs = reinterpret_cast<bf16*>(smem_raw);
-    bf16* ks = qs + BM * QS;
-    bf16* vs = ks + BN * KS;
+    bf16* ks_all = qs + BM * QS;           // two stages of keys
+    bf16* vs_all = ks_all + 2 * BN * KS;   // two stages of values
     const int en = blockIdx.y, g = MODE == 0 ? blockIdx.z : blockIdx.z / splits;
     const int sp = MODE == 0 ? 0 : blockIdx.z % splits;
     const int R = nh / nkv;
@@ -193,12 +197,25 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
 
     // ---- first walk: maxima and denominators of both maps
     float mx[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, den[2][2] = {{0.f, 0.f}, {0.f, 0.f}};  // [map][lo, hi]
-    for (int j0 = first_key; MODE != 2 && j0 <= last_key; j0 += BN) {
-        __syncthreads();  // the tile before is done with
-        load_tile(ks, vs, k_pool, v_pool, table, max_blocks, j0, last_key, g, nkv, page_size, num_pages, false, err);
-        cp_async_wait_all();
+    const int n_tiles = last_key >= first_key ? (last_key - first_key) / BN + 1 : 0;
+    if (MODE != 2 && n_tiles > 0) {
+        load_tile(ks_all, vs_all, k_pool, v_pool, table, max_blocks, first_key, last_key, g, nkv, page_size, num_pages,
+                  false, err);
+        cp_async_commit();
+    }
+    for (int t = 0; MODE != 2 && t < n_tiles; ++t) {
+        const int j0 = first_key + t * BN;
+        const bf16* ks = ks_all + (t & 1) * BN * KS;
+        if (t + 1 < n_tiles) {
+            load_tile(ks_all + ((t + 1) & 1) * BN * KS, vs_all, k_pool, v_pool, table, max_blocks, j0 + BN, last_key, g,
+                      nkv, page_size, num_pages, false, err);
+            cp_async_commit();
+            cp_async_wait_but_one();
+        } else {
+            cp_async_wait_all();
+        }
         __syncthreads();
-        if (j0 > warp_last_key) continue;  // (the whole warp)
+        if (j0 <= warp_last_key) {  // (the whole warp)
         float s[2][4][4];
         scores(s, qs_warp, ks, lane);
 #pragma unroll
@@ -238,6 +255,8 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
             mx[m][0] = n_lo;
             mx[m][1] = n_hi;
         }
+        }
+        __syncthreads();  // the stage is free for the tile after the next
     }
     if (MODE == 1) {
         cp_async_wait_all();  // (the queries, when the slice held no key)
@@ -290,13 +309,26 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
     const int v_key = ((lane >> 3) & 1) * 8 + (lane & 7), v_col = (lane >> 4) * 8;
-    if (MODE == 2 && first_key > last_key) cp_async_wait_all();  // (the queries; nothing else follows)
-    for (int j0 = first_key; j0 <= last_key; j0 += BN) {
+    if (MODE == 2 && n_tiles == 0) cp_async_wait_all();  // (the queries; nothing else follows)
+    if (n_tiles > 0) {
+        load_tile(ks_all, vs_all, k_pool, v_pool, table, max_blocks, first_key, last_key, g, nkv, page_size, num_pages,
+                  true, err);
+        cp_async_commit();
+    }
+    for (int t = 0; t < n_tiles; ++t) {
+        const int j0 = first_key + t * BN;
+        const bf16* ks = ks_all + (t & 1) * BN * KS;
+        const bf16* vs = vs_all + (t & 1) * BN * VS;
+        if (t + 1 < n_tiles) {
+            load_tile(ks_all + ((t + 1) & 1) * BN * KS, vs_all + ((t + 1) & 1) * BN * VS, k_pool, v_pool, table, max_blocks,
+                      j0 + BN, last_key, g, nkv, page_size, num_pages, true, err);
+            cp_async_commit();
+            cp_async_wait_but_one();
+        } else {
+            cp_async_wait_all();
+        }
         __syncthreads();
-        load_tile(ks, vs, k_pool, v_pool, table, max_blocks, j0, last_key, g, nkv, page_size, num_pages, true, err);
-        cp_async_wait_all();
-        __syncthreads();
-        if (j0 > warp_last_key) continue;
+        if (j0 <= warp_last_key) {
         float s[2][4][4];
         scores(s, qs_warp, ks, lane);
         unsigned w[4][2];  // [tile of 8 keys][lo, hi] as pairs of bf16
@@ -328,6 +360,8 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
                 mma_bf16(acc[2 * pr + 1], a, b2, b3);
             }
         }
+        }
+        __syncthreads();
     }
 
     if (MODE == 2) {
@@ -417,7 +451,7 @@ IB_EXPORT int ib_attention_diff_mma(const void* q, const void* k_pool, const voi
     if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !(eps > 0.f))
         return IB_ERR_BAD_ARG;
     if (n_entries > 65535 || nkv > 65535) return IB_ERR_TOO_LARGE;
-    const size_t smem = (size_t)(BM * QS + BN * KS + BN * VS) * sizeof(bf16);
+    const size_t smem = (size_t)(BM * QS + 2 * BN * KS + 2 * BN * VS) * sizeof(bf16);
     static bool configured = false;
     if (!configured) {
         cudaError_t ce = cudaFuncSetAttribute(attention_diff_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
