@@ -137,9 +137,13 @@ __device__ __forceinline__ void scores(float (&s)[2][4][4], const bf16* qs_warp,
     }
 }
 
+// cap * tanh(s * scale / cap) with tanh(x) = 1 - 2 / (exp(2 x) + 1) on the fast exponential and division
+// (absolute error of a score some 1e-7 of the cap; |x| beyond 15 is +-1 in 32-bit anyway).
 __device__ __forceinline__ float capped(float s, float scale, float cap, float inv_cap) {
     s *= scale;
-    return cap > 0.f ? cap * tanhf(s * inv_cap) : s;
+    if (cap <= 0.f) return s;
+    const float x = fminf(fmaxf(s * inv_cap, -15.f), 15.f);
+    return cap * (1.f - __fdividef(2.f, __expf(2.f * x) + 1.f));
 }
 
 // MODE 0: both walks over all keys, the normed result to `out`.  MODE 1: the first walk over the
@@ -147,7 +151,7 @@ __device__ __forceinline__ float capped(float s, float scale, float cap, float i
 // the slices' maxima and denominators merged, the second walk over the CTA's slice, its share
 // of w V to `part` [splits][rows][heads][E] (32-bit, not normed).
 template <int MODE>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                           bf16* __restrict__ out, const int* __restrict__ cu_rows, const int* __restrict__ positions,
                           const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int page_size,
@@ -165,7 +169,8 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
     const int R = nh / nkv;
     const int row0 = cu_rows[en], n_rows = cu_rows[en + 1] - row0;
     const int n_packed = n_rows * R;
-    const int tile0 = blockIdx.x * BM;
+    // (the row tiles that see the most keys start first)
+    const int tile0 = (int)(gridDim.x - 1 - blockIdx.x) * BM;
     if (tile0 >= n_packed) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gq = lane >> 2, tq = lane & 3;
@@ -243,7 +248,7 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
                 for (int i = 0; i < 4; ++i) {
                     const float v = s[m][n][i];
                     if (v != -INFINITY) {
-                        if (i >= 2) a_hi += expf(v - n_hi); else a_lo += expf(v - n_lo);
+                        if (i >= 2) a_hi += __expf(v - n_hi); else a_lo += __expf(v - n_lo);
                     }
                 }
             a_lo += __shfl_xor_sync(0xffffffffu, a_lo, 1);
@@ -341,8 +346,8 @@ attention_diff_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
                 const int h = i >> 1;
                 float v = 0.f;
                 if (j <= (h ? pos_hi : pos_lo)) {
-                    v = expf(capped(s[0][n][i], scale, cap, inv_cap) - mx[0][h]) * inv[0][h]
-                        + expf(capped(s[1][n][i], scale, cap, inv_cap) - mx[1][h]) * inv[1][h];
+                    v = __expf(capped(s[0][n][i], scale, cap, inv_cap) - mx[0][h]) * inv[0][h]
+                        + __expf(capped(s[1][n][i], scale, cap, inv_cap) - mx[1][h]) * inv[1][h];
                 }
                 wv[i] = v;
             }
@@ -415,8 +420,18 @@ __global__ void attention_diff_merge_kernel(const float* __restrict__ part, bf16
     for (int i = 0; i < PER; ++i) {
         const int c = lane + 32 * i;
         float a = 0.f;
-        if (c < E)
-            for (int k = 0; k < splits; ++k) a += part[((size_t)k * n_rows * nh + item) * E + c];
+        if (c < E) {
+            // four loads in flight; the sums are taken in slice order all the same
+            const size_t step = (size_t)n_rows * nh * E;
+            const float* src = part + (size_t)item * E + c;
+            int k = 0;
+            for (; k + 4 <= splits; k += 4) {
+                const float p0 = src[(size_t)k * step], p1 = src[(size_t)(k + 1) * step], p2 = src[(size_t)(k + 2) * step],
+                            p3 = src[(size_t)(k + 3) * step];
+                a = (((a + p0) + p1) + p2) + p3;
+            }
+            for (; k < splits; ++k) a += src[(size_t)k * step];
+        }
         v[i] = a;
         ss = fmaf(a, a, ss);
     }

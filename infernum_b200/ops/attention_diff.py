@@ -52,16 +52,27 @@ ROW_TILE, KEY_TILE, MAX_SPLITS = 64, 32, 64
 
 
 def choose_splits(max_rows_per_entry: int, n_entries: int, group: int, kv_heads: int, max_kv_len: int,
-                  sm_count: int) -> Tuple[int, int]:
-    """(slices of the keys, keys per slice).  One slice unless every entry fits one row tile, the CTAs
-    leave SMs idle and there are keys enough for slices of at least two tiles; then as many slices as
-    fill the SMs about four times (a CTA waits for its keys most of the time)."""
-    ctas = max(1, n_entries * kv_heads)
-    if max_rows_per_entry * group > ROW_TILE or ctas >= 2 * sm_count or max_kv_len < 4 * KEY_TILE:
-        return 1, 0
-    want = min(-(-4 * sm_count // ctas), max_kv_len // (2 * KEY_TILE), MAX_SPLITS, 65535 // max(kv_heads, 1))
-    if want < 2:
-        return 1, 0
+                  sm_count: int, n_rows: int = 0, heads: int = 0, vdim: int = 0) -> Tuple[int, int]:
+    """(slices of the keys, keys per slice).  Steps of few rows (every entry fits one row tile): when
+    the CTAs leave SMs idle and there are keys enough for slices of at least two tiles, as many slices
+    as fill the SMs about four times (a CTA waits for its keys most of the time).  Prompts: the row
+    tile at a prompt's end walks all its keys while the first walks one tile, and a prompt of a few
+    thousand tokens has no more row tiles than the SMs hold at once; slices of at least 512 keys
+    shorten that longest walk, as many as keep the slices' 32-bit shares (``n_rows x heads x vdim``
+    floats each) within 96 MB."""
+    tiles = -(-max_rows_per_entry * group // ROW_TILE)
+    ctas = max(1, tiles * n_entries * kv_heads)
+    if tiles > 1:
+        share = max(1, n_rows * heads * vdim * 4)
+        want = min(max_kv_len // 512, 8, (96 << 20) // share, 65535 // max(kv_heads, 1))
+        if want < 2 or ctas >= 8 * sm_count:
+            return 1, 0
+    else:
+        if ctas >= 2 * sm_count or max_kv_len < 4 * KEY_TILE:
+            return 1, 0
+        want = min(-(-4 * sm_count // ctas), max_kv_len // (2 * KEY_TILE), MAX_SPLITS, 65535 // max(kv_heads, 1))
+        if want < 2:
+            return 1, 0
     slice_len = -(-(-(-max_kv_len // want)) // KEY_TILE) * KEY_TILE
     return -(-max_kv_len // slice_len), slice_len
 
@@ -87,7 +98,7 @@ def run(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.
         forced = rt.options.get("diff_splits")
         plan = tuple(forced) if forced else choose_splits(
             ctx.max_rows_per_entry, ctx.n_entries, n_heads // nkv, nkv, getattr(ctx, "max_kv_len", 0),
-            rt.options.get("sm_count") or SM_COUNT_FALLBACK)
+            rt.options.get("sm_count") or SM_COUNT_FALLBACK, N, n_heads, vdim)
         if hasattr(ctx, "scratch"):
             ctx.scratch[key] = plan
     splits, slice_len = plan

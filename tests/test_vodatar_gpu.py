@@ -592,7 +592,10 @@ def test_two_score_maps_on_the_tensor_cores(H, G, d, e, page):
 
 def test_slices_of_the_keys_are_chosen_for_steps_of_few_rows():
     from infernum_b200.ops.attention_diff import choose_splits
-    assert choose_splits(512, 1, 4, 2, 2048, 148) == (1, 0)          # a prompt: row tiles fill the machine
+    assert choose_splits(300, 1, 4, 2, 300, 148, 300, 8, 64) == (1, 0)  # a short prompt
+    splits, slice_len = choose_splits(2048, 1, 4, 2, 2048, 148, 2048, 8, 256)  # a prompt whose last rows see many keys
+    assert splits == 4 and slice_len == 512
+    assert choose_splits(16384, 4, 4, 2, 16384, 148, 65536, 8, 256) == (1, 0)  # row tiles enough, shares too large
     assert choose_splits(1, 128, 4, 4, 1024, 148) == (1, 0)          # many decoded rows: CTAs enough
     assert choose_splits(1, 8, 4, 2, 100, 148) == (1, 0)             # few keys
     for entries, kv_heads, keys in ((1, 2, 1024), (8, 2, 1024), (1, 1, 9000), (3, 4, 300)):
