@@ -120,10 +120,11 @@ __device__ __forceinline__ void scores(float (&s)[2][4][4], const bf16* qs_warp,
             for (int i = 0; i < 4; ++i) s[m][n][i] = 0.f;
     const int a_row = lane & 15, a_col = (lane >> 4) * 8;
     const int b_key = ((lane >> 4) * 8) + (lane & 7), b_col = ((lane >> 3) & 1) * 8;
-#pragma unroll
-    for (int m = 0; m < 2; ++m) {
+    // (the two maps side by side in every step: eight accumulators between two uses of one)
 #pragma unroll 4
-        for (int kk = 0; kk < D / 16; ++kk) {
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
             unsigned a[4];
             ldsm_x4(a[0], a[1], a[2], a[3], qs_warp + a_row * QS + m * D + kk * 16 + a_col);
 #pragma unroll
@@ -443,6 +444,228 @@ __global__ void attention_diff_merge_kernel(const float* __restrict__ part, bf16
         if (c < E) out[(size_t)item * E + c] = __float2bfloat16_rn(v[i] * f);
     }
 }
+
+// ---- entries of at most 16 packed rows (decoded tokens): one walk ----------------------------
+// Every warp computes both maps' scores of the same 16 rows against the tile and owns a quarter of
+// the value's columns, for which it keeps both maps' running sums (two accumulators of E / 4 columns
+// fit).  A CTA takes one slice of an entry's keys and writes, per row and head, both maps' maxima and
+// denominators and both unnormed sums in 32-bit; the merge below weighs the slices and takes the
+// difference.  The keys are read once.
+constexpr int NT_W = E >= 64 ? E / 32 : 2;  // accumulator tiles of a warp's quarter (E a multiple of 64; else not run)
+
+__global__ void __launch_bounds__(THREADS, 2)
+attention_diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
+                             const int* __restrict__ cu_rows, const int* __restrict__ positions,
+                             const int* __restrict__ block_tables, int max_blocks, int nh, int nkv, int page_size,
+                             int num_pages, float scale, float cap, unsigned* __restrict__ err, int splits, int slice_len,
+                             int n_total_rows, float* __restrict__ stats, float* __restrict__ part) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* qs = reinterpret_cast<bf16*>(smem_raw);
+    bf16* ks_all = qs + 16 * QS;
+    bf16* vs_all = ks_all + 2 * BN * KS;
+    const int en = blockIdx.y, g = blockIdx.z / splits, sp = blockIdx.z % splits;
+    const int R = nh / nkv;
+    const int row0 = cu_rows[en], n_rows = cu_rows[en + 1] - row0;
+    const int n_packed = min(n_rows * R, 16);
+    if (n_packed <= 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gq = lane >> 2, tq = lane & 3;
+    const int* table = block_tables + (size_t)en * max_blocks;
+    const int pos0 = positions[row0];
+    const int last_seen = pos0 + (n_packed - 1) / R;
+    const int first_key = sp * slice_len;
+    const int last_key = min(last_seen, first_key + slice_len - 1);
+    {
+        constexpr int QC = KW / 8;
+        for (int c = threadIdx.x; c < 16 * QC; c += THREADS) {
+            const int r = c / QC, part_i = c % QC;
+            bf16* dst = qs + r * QS + part_i * 8;
+            if (r < n_packed)
+                cp_async16(dst, q + ((size_t)(row0 + r / R) * nh + g * R + r % R) * KW + part_i * 8);
+            else
+                *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+        }
+    }
+    const int p_lo = gq, p_hi = gq + 8;
+    const int pos_lo = p_lo < n_packed ? pos0 + p_lo / R : -1, pos_hi = p_hi < n_packed ? pos0 + p_hi / R : -1;
+    const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+    float mx[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, den[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    float acc[2][NT_W][4];
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int n = 0; n < NT_W; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
+    const int v_key = ((lane >> 3) & 1) * 8 + (lane & 7), v_col = warp * (E / 4) + (lane >> 4) * 8;
+    const int n_tiles = last_key >= first_key ? (last_key - first_key) / BN + 1 : 0;
+    if (n_tiles > 0) {
+        load_tile(ks_all, vs_all, k_pool, v_pool, table, max_blocks, first_key, last_key, g, nkv, page_size, num_pages,
+                  true, err);
+        cp_async_commit();
+    } else {
+        cp_async_wait_all();
+    }
+    for (int t = 0; t < n_tiles; ++t) {
+        const int j0 = first_key + t * BN;
+        const bf16* ks = ks_all + (t & 1) * BN * KS;
+        const bf16* vs = vs_all + (t & 1) * BN * VS;
+        if (t + 1 < n_tiles) {
+            load_tile(ks_all + ((t + 1) & 1) * BN * KS, vs_all + ((t + 1) & 1) * BN * VS, k_pool, v_pool, table, max_blocks,
+                      j0 + BN, last_key, g, nkv, page_size, num_pages, true, err);
+            cp_async_commit();
+            cp_async_wait_but_one();
+        } else {
+            cp_async_wait_all();
+        }
+        __syncthreads();
+        float s[2][4][4];
+        scores(s, qs, ks, lane);
+        unsigned w[2][4][2];  // [map][tile of 8 keys][lo, hi]: the probabilities as pairs of bf16
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            float t_lo = -INFINITY, t_hi = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int j = j0 + n * 8 + 2 * tq + (i & 1);
+                    const bool hi = i >= 2;
+                    const float v = j <= (hi ? pos_hi : pos_lo) ? capped(s[m][n][i], scale, cap, inv_cap) : -INFINITY;
+                    s[m][n][i] = v;
+                    if (hi) t_hi = fmaxf(t_hi, v); else t_lo = fmaxf(t_lo, v);
+                }
+            t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 1));
+            t_lo = fmaxf(t_lo, __shfl_xor_sync(0xffffffffu, t_lo, 2));
+            t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 1));
+            t_hi = fmaxf(t_hi, __shfl_xor_sync(0xffffffffu, t_hi, 2));
+            const float n_lo = fmaxf(mx[m][0], t_lo), n_hi = fmaxf(mx[m][1], t_hi);
+            const float c_lo = n_lo == -INFINITY ? 0.f : __expf(mx[m][0] - n_lo);  // (exp(-inf) = 0 on the first keys)
+            const float c_hi = n_hi == -INFINITY ? 0.f : __expf(mx[m][1] - n_hi);
+            float a_lo = 0.f, a_hi = 0.f;
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                float pv[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float v = s[m][n][i];
+                    pv[i] = v == -INFINITY ? 0.f : __expf(v - (i >= 2 ? n_hi : n_lo));
+                }
+                a_lo += pv[0] + pv[1];
+                a_hi += pv[2] + pv[3];
+                w[m][n][0] = pack_bf16(pv[0], pv[1]);
+                w[m][n][1] = pack_bf16(pv[2], pv[3]);
+            }
+            a_lo += __shfl_xor_sync(0xffffffffu, a_lo, 1);
+            a_lo += __shfl_xor_sync(0xffffffffu, a_lo, 2);
+            a_hi += __shfl_xor_sync(0xffffffffu, a_hi, 1);
+            a_hi += __shfl_xor_sync(0xffffffffu, a_hi, 2);
+            den[m][0] = den[m][0] * c_lo + a_lo;
+            den[m][1] = den[m][1] * c_hi + a_hi;
+            mx[m][0] = n_lo;
+            mx[m][1] = n_hi;
+#pragma unroll
+            for (int n = 0; n < NT_W; ++n) {
+                acc[m][n][0] *= c_lo;
+                acc[m][n][1] *= c_lo;
+                acc[m][n][2] *= c_hi;
+                acc[m][n][3] *= c_hi;
+            }
+        }
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            const unsigned a1[4] = {w[0][2 * kk][0], w[0][2 * kk][1], w[0][2 * kk + 1][0], w[0][2 * kk + 1][1]};
+            const unsigned a2[4] = {w[1][2 * kk][0], w[1][2 * kk][1], w[1][2 * kk + 1][0], w[1][2 * kk + 1][1]};
+#pragma unroll
+            for (int pr = 0; pr < NT_W / 2; ++pr) {
+                unsigned b0, b1, b2, b3;
+                ldsm_x4_trans(b0, b1, b2, b3, vs + (kk * 16 + v_key) * VS + pr * 16 + v_col);
+                mma_bf16(acc[0][2 * pr], a1, b0, b1);
+                mma_bf16(acc[0][2 * pr + 1], a1, b2, b3);
+                mma_bf16(acc[1][2 * pr], a2, b0, b1);
+                mma_bf16(acc[1][2 * pr + 1], a2, b2, b3);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int p = h ? p_hi : p_lo;
+        if (p >= n_packed) continue;
+        const size_t item = ((size_t)sp * n_total_rows + row0 + p / R) * nh + g * R + p % R;
+        if (warp == 0 && tq == 0) {
+            float* dst = stats + item * 4;
+            dst[0] = mx[0][h];
+            dst[1] = den[0][h];
+            dst[2] = mx[1][h];
+            dst[3] = den[1][h];
+        }
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            float* dst = part + (item * 2 + m) * E + warp * (E / 4);
+#pragma unroll
+            for (int n = 0; n < NT_W; ++n)
+                *reinterpret_cast<float2*>(dst + n * 8 + 2 * tq) = make_float2(acc[m][n][2 * h], acc[m][n][2 * h + 1]);
+        }
+    }
+}
+
+// The slices of the kernel above weighed by their maxima, the difference of the two maps, the norm.
+__global__ void attention_diff_decode_merge_kernel(const float* __restrict__ stats, const float* __restrict__ part,
+                                                   bf16* __restrict__ out, int splits, int n_rows, int nh, float lambda,
+                                                   float eps, float out_scale) {
+    pdl_trigger();
+    pdl_wait();
+    const int item = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (item >= n_rows * nh) return;
+    const size_t step = (size_t)n_rows * nh;
+    float best[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f};
+    for (int k = 0; k < splits; ++k) {
+        best[0] = fmaxf(best[0], stats[(k * step + item) * 4]);
+        best[1] = fmaxf(best[1], stats[(k * step + item) * 4 + 2]);
+    }
+    constexpr int PER = (E + 31) / 32;
+    float v[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) v[i] = 0.f;
+    float o[2][PER];
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int i = 0; i < PER; ++i) o[m][i] = 0.f;
+    for (int k = 0; k < splits; ++k) {
+        const float* st = stats + (k * step + item) * 4;
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            const float mk = st[2 * m];
+            if (mk == -INFINITY) continue;  // (the slice held no key of this row)
+            const float f = expf(mk - best[m]);
+            sum[m] += st[2 * m + 1] * f;
+            const float* src = part + ((k * step + item) * 2 + m) * E;
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                const int c = lane + 32 * i;
+                if (c < E) o[m][i] = fmaf(src[c], f, o[m][i]);
+            }
+        }
+    }
+    const float i1 = sum[0] > 0.f ? 1.f / sum[0] : 0.f, i2 = sum[1] > 0.f ? -lambda / sum[1] : 0.f;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        v[i] = lane + 32 * i < E ? o[0][i] * i1 + o[1][i] * i2 : 0.f;
+        ss = fmaf(v[i], v[i], ss);
+    }
+    ss = warp_sum(ss);
+    const float f = out_scale / sqrtf(ss / (float)E + eps);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = lane + 32 * i;
+        if (c < E) out[(size_t)item * E + c] = __float2bfloat16_rn(v[i] * f);
+    }
+}
 }  // namespace
 
 IB_EXPORT int ib_attention_diff_mma_d() { return D; }
@@ -506,6 +729,49 @@ IB_EXPORT int ib_attention_diff_mma(const void* q, const void* k_pool, const voi
     const long long warps = (long long)n_rows * nh;
     le = launch_kernel(attention_diff_merge_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, s, (const float*)part,
                        (bf16*)out, splits, n_rows, nh, eps, out_scale);
+    if (le != cudaSuccess) return (int)le;
+    IB_LAUNCH_CHECK();
+    return IB_OK;
+}
+
+// Steps whose entries all have at most 16 packed rows (rows x heads of a group) and values a multiple of 64
+// wide: the one-walk kernel over `splits` slices of `slice_len` keys (a multiple of 32) and its merge.
+IB_EXPORT long long ib_attention_diff_decode_scratch_bytes(int n_rows, int nh, int splits) {
+    return (long long)splits * n_rows * nh * (4 + 2 * E) * (long long)sizeof(float);
+}
+
+IB_EXPORT int ib_attention_diff_decode(const void* q, const void* k_pool, const void* v_pool, void* out, const int* cu_rows,
+                                       const int* positions, const int* block_tables, int max_blocks, int n_entries,
+                                       int nh, int nkv, int page_size, int num_pages, float scale, float cap, float lambda,
+                                       float eps, float out_scale, unsigned* err, int n_rows, int splits, int slice_len,
+                                       void* scratch, long long scratch_bytes, void* stream) {
+    if (n_entries <= 0 || n_rows <= 0) return IB_OK;
+    if (E % 64) return IB_ERR_UNSUPPORTED;
+    if (!q || !k_pool || !v_pool || !out || !cu_rows || !positions || !block_tables || !err || !scratch)
+        return IB_ERR_BAD_ARG;
+    if (nh <= 0 || nkv <= 0 || nh % nkv || page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !(eps > 0.f) ||
+        splits <= 0 || slice_len <= 0 || slice_len % BN)
+        return IB_ERR_BAD_ARG;
+    if (n_entries > 65535 || (long long)nkv * splits > 65535) return IB_ERR_TOO_LARGE;
+    if (scratch_bytes < ib_attention_diff_decode_scratch_bytes(n_rows, nh, splits)) return IB_ERR_BAD_ARG;
+    const size_t smem = (size_t)(16 * QS + 2 * BN * KS + 2 * BN * VS) * sizeof(bf16);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t ce = cudaFuncSetAttribute(attention_diff_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (ce != cudaSuccess) return (int)ce;
+        configured = true;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    float* stats = (float*)scratch;
+    float* part = stats + (size_t)splits * n_rows * nh * 4;
+    cudaError_t le = launch_kernel(attention_diff_decode_kernel, dim3(1, n_entries, nkv * splits), dim3(THREADS), smem, s,
+                                   (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, cu_rows, positions, block_tables,
+                                   max_blocks, nh, nkv, page_size, num_pages, scale, cap, err, splits, slice_len, n_rows, stats,
+                                   part);
+    if (le != cudaSuccess) return (int)le;
+    const long long warps = (long long)n_rows * nh;
+    le = launch_kernel(attention_diff_decode_merge_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, s,
+                       (const float*)stats, (const float*)part, (bf16*)out, splits, n_rows, nh, lambda, eps, out_scale);
     if (le != cudaSuccess) return (int)le;
     IB_LAUNCH_CHECK();
     return IB_OK;

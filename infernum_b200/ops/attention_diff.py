@@ -7,8 +7,11 @@ the caller then takes the plain 32-bit kernel (``core.attention_diff``).
 
 A step whose entries all have few rows (decoded tokens) would run one CTA per
 entry and key/value head; ``choose_splits`` then cuts the keys in slices over
-several CTAs (two launches and a merge).  The plan and the scratch buffer are
-worked out once per step and kept in ``ctx.scratch``.
+several CTAs.  When every entry has at most 16 packed rows (rows x heads of a
+group) and values are a multiple of 64 wide, a kernel that walks the keys once
+with both maps' sums side by side takes the step (``one_walk``); otherwise the
+two walks become two launches.  The plan and the scratch buffer are worked out
+once per step and kept in ``ctx.scratch``.
 """
 
 from __future__ import annotations
@@ -41,6 +44,13 @@ def lib_for(dim: int, vdim: int) -> ctypes.CDLL:
         lib.ib_attention_diff_mma.restype = _c_int
         lib.ib_attention_diff_mma_scratch_bytes.argtypes = [_c_int, _c_int, _c_int]
         lib.ib_attention_diff_mma_scratch_bytes.restype = ctypes.c_longlong
+        lib.ib_attention_diff_decode.argtypes = [
+            _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+            _c_int, _c_int, _c_float, _c_float, _c_float, _c_float, _c_float, _c_void_p, _c_int, _c_int, _c_int,
+            _c_void_p, ctypes.c_longlong, _c_void_p]
+        lib.ib_attention_diff_decode.restype = _c_int
+        lib.ib_attention_diff_decode_scratch_bytes.argtypes = [_c_int, _c_int, _c_int]
+        lib.ib_attention_diff_decode_scratch_bytes.restype = ctypes.c_longlong
         if lib.ib_attention_diff_mma_d() != dim or lib.ib_attention_diff_mma_e() != vdim:
             raise KernelError(f"differential attention module for ({dim}, {vdim}) was built for other sizes")
         _libs[(dim, vdim)] = lib
@@ -77,6 +87,11 @@ def choose_splits(max_rows_per_entry: int, n_entries: int, group: int, kv_heads:
     return -(-max_kv_len // slice_len), slice_len
 
 
+def one_walk(max_rows_per_entry: int, group: int, vdim: int) -> bool:
+    """Whether the kernel that walks the keys once takes the step."""
+    return max_rows_per_entry * group <= 16 and vdim % 64 == 0
+
+
 def run(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, ctx, tables: torch.Tensor,
         n_heads: int, scale: float, softcap: float, lam: float, eps: float, out_scale: float, rt) -> bool:
     """Arguments as ``core.attention_diff``; entries and their rows come from ``ctx.cu_rows`` and
@@ -101,16 +116,30 @@ def run(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.
             rt.options.get("sm_count") or SM_COUNT_FALLBACK, N, n_heads, vdim)
         if hasattr(ctx, "scratch"):
             ctx.scratch[key] = plan
-    splits, slice_len = plan
+    splits, slice_len = plan[:2]
+    once = bool(plan[2]) if len(plan) > 2 else one_walk(ctx.max_rows_per_entry, n_heads // nkv, vdim)
+    if once and (splits <= 1 and slice_len <= 0):
+        # one slice over all keys any row of the step sees
+        splits, slice_len = 1, max(KEY_TILE, -(-ctx.max_kv_len // KEY_TILE) * KEY_TILE)
     scratch_ptr, scratch_bytes = None, 0
-    if splits > 1:
-        need = lib.ib_attention_diff_mma_scratch_bytes(N, n_heads, splits)
+    if splits > 1 or once:
+        need = (lib.ib_attention_diff_decode_scratch_bytes if once else lib.ib_attention_diff_mma_scratch_bytes)(
+            N, n_heads, splits)
         buf = ctx.scratch.get("diff_split") if hasattr(ctx, "scratch") else None
         if buf is None or buf.numel() * 4 < need:
             buf = torch.empty((need + 3) // 4, dtype=torch.float32, device=q.device)
             if hasattr(ctx, "scratch"):
                 ctx.scratch["diff_split"] = buf
         scratch_ptr, scratch_bytes = buf.data_ptr(), buf.numel() * 4
+    if once:
+        code = lib.ib_attention_diff_decode(
+            q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), ctx.cu_rows.data_ptr(),
+            ctx.positions.data_ptr(), tables.data_ptr(), tables.shape[1], ctx.n_entries, n_heads, nkv, page_size,
+            num_pages, float(scale), float(softcap or 0.0), float(lam), float(eps), float(out_scale), rt.err.data_ptr(),
+            N, splits, slice_len, scratch_ptr, scratch_bytes, core.stream_ptr(q))
+        core.check(code, "attention_diff_decode")
+        core.profile_mark("attention_diff_decode")
+        return True
     code = lib.ib_attention_diff_mma(
         q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(), ctx.cu_rows.data_ptr(),
         ctx.positions.data_ptr(), tables.data_ptr(), tables.shape[1], ctx.n_entries, ctx.max_rows_per_entry, n_heads, nkv,

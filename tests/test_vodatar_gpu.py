@@ -584,10 +584,19 @@ def test_two_score_maps_on_the_tensor_cores(H, G, d, e, page):
     # behind a sequence's last key, a slice of one tile, as many slices as there are tiles
     lens = [1, 2, 33, 64, 301, 300, 97, 129]
     rows = [1, 2, 1, 3, 1, 2, 0, 1]
-    for plan in ((2, 160), (5, 64), (10, 32), (3, 128)):
+    for plan in ((2, 160, 0), (5, 64, 0), (10, 32, 0), (3, 128, 0)):
         rt.options["diff_splits"] = plan
         check_two_maps(torch.bfloat16, H, G, d, e, page, lens, rows, run, 3e-2)
     assert int(rt.err.item()) == 0
+    # entries of at most 16 packed rows and values a multiple of 64 wide: the keys walked once, both maps'
+    # sums side by side, in one slice and in several
+    from infernum_b200.ops.attention_diff import one_walk
+    rows = [1, 2, 1, 16 // (H // G), 1, min(2, 16 // (H // G)), 0, 1]
+    if one_walk(max(rows), H // G, e):
+        for plan in ((1, 320, 1), (2, 160, 1), (5, 64, 1), (10, 32, 1)):
+            rt.options["diff_splits"] = plan
+            check_two_maps(torch.bfloat16, H, G, d, e, page, lens, rows, run, 3e-2)
+        assert int(rt.err.item()) == 0
 
 
 def test_slices_of_the_keys_are_chosen_for_steps_of_few_rows():
