@@ -612,37 +612,37 @@ attention_diff_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict_
     }
 }
 
-// The slices of the kernel above weighed by their maxima, the difference of the two maps, the norm.
+// The slices of the kernel above weighed by their maxima, the difference of the two maps, the norm: a CTA
+// of four warps per (row, head); warp w adds the slices w, w + 4, ... and the four sums meet in shared
+// memory in warp order.
 __global__ void attention_diff_decode_merge_kernel(const float* __restrict__ stats, const float* __restrict__ part,
                                                    bf16* __restrict__ out, int splits, int n_rows, int nh, float lambda,
                                                    float eps, float out_scale) {
     pdl_trigger();
     pdl_wait();
-    const int item = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (item >= n_rows * nh) return;
+    __shared__ float sh_o[4][2][E];
+    __shared__ float sh_sum[4][2];
+    __shared__ float sh_ss[4];
+    const int item = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t step = (size_t)n_rows * nh;
-    float best[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f};
+    float best[2] = {-INFINITY, -INFINITY};
     for (int k = 0; k < splits; ++k) {
         best[0] = fmaxf(best[0], stats[(k * step + item) * 4]);
         best[1] = fmaxf(best[1], stats[(k * step + item) * 4 + 2]);
     }
     constexpr int PER = (E + 31) / 32;
-    float v[PER];
-#pragma unroll
-    for (int i = 0; i < PER; ++i) v[i] = 0.f;
-    float o[2][PER];
+    float o[2][PER], sum[2] = {0.f, 0.f};
 #pragma unroll
     for (int m = 0; m < 2; ++m)
 #pragma unroll
         for (int i = 0; i < PER; ++i) o[m][i] = 0.f;
-    for (int k = 0; k < splits; ++k) {
+    for (int k = warp; k < splits; k += 4) {
         const float* st = stats + (k * step + item) * 4;
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
             const float mk = st[2 * m];
-            if (mk == -INFINITY) continue;  // (the slice held no key of this row)
-            const float f = expf(mk - best[m]);
-            sum[m] += st[2 * m + 1] * f;
+            const float f = mk == -INFINITY ? 0.f : expf(mk - best[m]);  // (-inf: the slice held no key of this row)
+            sum[m] = fmaf(st[2 * m + 1], f, sum[m]);
             const float* src = part + ((k * step + item) * 2 + m) * E;
 #pragma unroll
             for (int i = 0; i < PER; ++i) {
@@ -651,18 +651,41 @@ __global__ void attention_diff_decode_merge_kernel(const float* __restrict__ sta
             }
         }
     }
-    const float i1 = sum[0] > 0.f ? 1.f / sum[0] : 0.f, i2 = sum[1] > 0.f ? -lambda / sum[1] : 0.f;
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+        if (lane == 0) sh_sum[warp][m] = sum[m];
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            const int c = lane + 32 * i;
+            if (c < E) sh_o[warp][m][c] = o[m][i];
+        }
+    }
+    __syncthreads();
+    const float s1 = ((sh_sum[0][0] + sh_sum[1][0]) + sh_sum[2][0]) + sh_sum[3][0];
+    const float s2 = ((sh_sum[0][1] + sh_sum[1][1]) + sh_sum[2][1]) + sh_sum[3][1];
+    const float i1 = s1 > 0.f ? 1.f / s1 : 0.f, i2 = s2 > 0.f ? -lambda / s2 : 0.f;
+    constexpr int MINE = (E + 127) / 128;
+    float v[MINE];
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-        v[i] = lane + 32 * i < E ? o[0][i] * i1 + o[1][i] * i2 : 0.f;
+    for (int i = 0; i < MINE; ++i) {
+        const int c = threadIdx.x + 128 * i;
+        v[i] = 0.f;
+        if (c < E) {
+            const float a1 = ((sh_o[0][0][c] + sh_o[1][0][c]) + sh_o[2][0][c]) + sh_o[3][0][c];
+            const float a2 = ((sh_o[0][1][c] + sh_o[1][1][c]) + sh_o[2][1][c]) + sh_o[3][1][c];
+            v[i] = a1 * i1 + a2 * i2;
+        }
         ss = fmaf(v[i], v[i], ss);
     }
     ss = warp_sum(ss);
+    if (lane == 0) sh_ss[warp] = ss;
+    __syncthreads();
+    ss = ((sh_ss[0] + sh_ss[1]) + sh_ss[2]) + sh_ss[3];
     const float f = out_scale / sqrtf(ss / (float)E + eps);
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-        const int c = lane + 32 * i;
+    for (int i = 0; i < MINE; ++i) {
+        const int c = threadIdx.x + 128 * i;
         if (c < E) out[(size_t)item * E + c] = __float2bfloat16_rn(v[i] * f);
     }
 }
@@ -769,8 +792,7 @@ IB_EXPORT int ib_attention_diff_decode(const void* q, const void* k_pool, const 
                                    max_blocks, nh, nkv, page_size, num_pages, scale, cap, err, splits, slice_len, n_rows, stats,
                                    part);
     if (le != cudaSuccess) return (int)le;
-    const long long warps = (long long)n_rows * nh;
-    le = launch_kernel(attention_diff_decode_merge_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, s,
+    le = launch_kernel(attention_diff_decode_merge_kernel, dim3((unsigned)((long long)n_rows * nh)), dim3(128), 0, s,
                        (const float*)stats, (const float*)part, (bf16*)out, splits, n_rows, nh, lambda, eps, out_scale);
     if (le != cudaSuccess) return (int)le;
     IB_LAUNCH_CHECK();
