@@ -435,12 +435,12 @@ def bolovik_prefill_flops(cfg: dict, T: int) -> float:
     return total + 2.0 * D * cfg["vocab"]
 
 
-def vodatar_config(width, layers, heads, kv_heads, ff, vocab, experts=16, top=4, identity=2):
+def vodatar_config(width, layers, heads, kv_heads, ff, vocab, experts=16, top=4, identity=1):
     """Layers in fours: attention through a latent (heads of 128 + 64 rotated, values of 128, a latent of
     512, frequencies on a ramp), then three layers of differential attention (half the heads, two maps
     of 128 each, values of 256, a convolution of 4 taps, scores capped at 50); every layer with a
     mixture of experts whose chosen experts do half a dense layer's work (an expert has ff / (2 top)
-    columns; two more router outputs hand the input on) beside a shared expert that does the other
+    columns; one more router output hands the input on) beside a shared expert that does the other
     half.  The first two layers are walked twice, so ``layers`` runs come from ``layers - 2`` layers."""
     lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
            "rot": {"dims": 64, "base": 10000.0,

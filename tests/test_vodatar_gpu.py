@@ -101,7 +101,7 @@ def compare(steps, out, seqs, plain, dtype, name, slack=1):
             fed[rid] += n
         for rid in s.get("end", []):
             fed[rid] = 0
-    assert len(errs) >= min(5, (len(errs) + skipped) // 10), f"{len(errs)} positions compared, {skipped} left out"
+    assert len(errs) >= min(3, (len(errs) + skipped) // 10), f"{len(errs)} positions compared, {skipped} left out"
     errs = np.sort(np.array(errs))
     tol = TOL[dtype] * slack
     over = int((errs > tol).sum())
@@ -422,7 +422,7 @@ def cuts_of(T, sizes):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("W,parts", [(96, 3), (72, 1), (320, 4), (64, 64), (1024, 4), (30, 2)])
+@pytest.mark.parametrize("W,parts", [(96, 3), (72, 1), (384, 6), (64, 64), (1024, 4), (30, 2)])
 def test_gated_result_normed_in_parts_and_added_with_a_factor(dtype, W, parts):
     from infernum_b200.ops import core
     g = torch.Generator().manual_seed(W + parts)
@@ -451,18 +451,22 @@ def test_gated_result_normed_in_parts_and_added_with_a_factor(dtype, W, parts):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("C,taps,add", [(40, 3, True), (7, 1, True), (130, 4, False), (64, 2, False), (33, 5, True)])
-def test_causal_convolution_over_steps_and_slots(dtype, C, taps, add):
+@pytest.mark.parametrize("C,taps,add,off,pad", [(40, 3, True, 11, 3), (7, 1, True, 11, 3), (130, 4, False, 11, 3),
+                                                (64, 2, False, 11, 3), (33, 5, True, 11, 3), (40, 3, True, 16, 8),
+                                                (64, 4, False, 32, 0), (8, 1, True, 16, 8), (256, 5, True, 16, 24)])
+def test_causal_convolution_over_steps_and_slots(dtype, C, taps, add, off, pad):
     """Two sequences cut differently and fed in the same steps, their states in slots that are
-    not neighbours; portions shorter than the taps; a slot used again after it was zeroed."""
+    not neighbours; portions shorter than the taps; a slot used again after it was zeroed.  ``off``
+    floats lie before the state in a slot and rows are ``pad`` wider than the channels: with multiples
+    of 8 everywhere the bfloat16 kernel takes eight channels a thread."""
     from infernum_b200.ops import core
     g = torch.Generator().manual_seed(C * taps)
     w = torch.randn(C, taps, generator=g)
     T = [37, 22]
     u = [torch.randn(t, C, generator=g).to(dtype) for t in T]
     ref = [pv.causal_conv(x.double(), w.double()) + (x.double() if add else 0) for x in u]
-    state = torch.zeros(5, 11 + max(taps - 1, 1) * C, dtype=torch.float32, device=DEV)
-    state[:, :11] = 7.0  # what lies before the offset is not the convolution's
+    state = torch.zeros(5, off + max(taps - 1, 1) * C, dtype=torch.float32, device=DEV)
+    state[:, :off] = 7.0  # what lies before the offset is not the convolution's
     for attempt in range(2):
         cuts = [cuts_of(T[0], [5, 1, 2, 9, 1, 1, 3]), cuts_of(T[1], [1, 1, 6, 2])]
         got = [torch.zeros(t, C, dtype=dtype) for t in T]
@@ -471,19 +475,19 @@ def test_causal_convolution_over_steps_and_slots(dtype, C, taps, add):
             rows = [cuts[s][i][1] for s in live]
             step = Step(rows, [[3, 1][s] for s in live])
             x = torch.cat([u[s][cuts[s][i][0]: cuts[s][i][0] + cuts[s][i][1]] for s in live]).to(DEV)
-            wide = torch.zeros(x.shape[0], C + 3, dtype=dtype, device=DEV)  # rows wider than the channels
+            wide = torch.zeros(x.shape[0], C + pad, dtype=dtype, device=DEV)  # rows wider than the channels
             wide[:, :C] = x
             out = torch.empty(x.shape[0], C, dtype=dtype, device=DEV)
-            core.causal_conv(wide[:, :C], w.to(DEV), state, 11, step, out, add_input=add)
-            core.conv_state_update(wide[:, :C], taps, state, 11, step)
+            core.causal_conv(wide[:, :C], w.to(DEV), state, off, step, out, add_input=add)
+            core.conv_state_update(wide[:, :C], taps, state, off, step)
             at = 0
             for s, n in zip(live, rows):
                 got[s][cuts[s][i][0]: cuts[s][i][0] + n] = out[at: at + n].cpu()
                 at += n
         for s in range(2):
             assert rel_err(got[s], ref[s]) < PART_TOL[dtype], f"sequence {s}, attempt {attempt}"
-        assert float(state[:, :11].min()) == 7.0 and float(state[[0, 2, 4]].abs()[:, 11:].max()) == 0.0
-        state[[1, 3], 11:] = 0.0  # the slots are given to new requests
+        assert float(state[:, :off].min()) == 7.0 and float(state[[0, 2, 4]].abs()[:, off:].max()) == 0.0
+        state[[1, 3], off:] = 0.0  # the slots are given to new requests
 
 
 def build_pools(keys, values, page_size, dtype, seed):
@@ -614,7 +618,7 @@ def test_slices_of_the_keys_are_chosen_for_steps_of_few_rows():
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,e,taps,rd", [(4, 2, 16, 24, 4, 8), (1, 1, 12, 12, 0, 12), (3, 3, 10, 6, 1, 0),
-                                            (2, 1, 8, 40, 5, 4), (4, 2, 32, 64, 3, 32)])
+                                            (2, 1, 8, 40, 5, 4), (4, 2, 48, 64, 3, 48)])
 def test_convolution_rotation_and_cache_write_of_two_map_attention(dtype, H, G, d, e, taps, rd):
     """A sequence fed in portions: queries, and the keys and values found in the pages afterwards,
     against the convolution and the rotation of neighbouring pairs applied to the whole sequence."""

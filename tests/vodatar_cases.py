@@ -86,7 +86,7 @@ CASE_D = {
     "canon": {"taps": 4}, "loop": {"start": 0, "stop": 2, "times": 2},
     "layers": [
         latent(4, 32, 32, 48, 64, 0.12, rot(32, 10000.0, (2.0, 128, 32.0, 1.0)), moe(64, 8, 3, 2, 128)),
-        attention(4, 2, 32, 64, 0.18, 20.0, 0.3, 4, rot(32, 20000.0), moe(64, 8, 4, 2, 64)),
+        attention(6, 2, 48, 64, 0.15, 25.0, 0.2, 4, rot(24, 30000.0), moe(64, 8, 4, 2, 64)),
         attention(8, 2, 16, 32, 0.25, 10.0, 0.1, 3, rot(8, 5000.0), moe(64, 4, 2, 0, 64)),
     ],
 }
@@ -108,7 +108,7 @@ def random_case(seed: int) -> dict:
     with and without outputs that hand the input on, shared experts, layers without a feed-forward."""
     import random
     rng = random.Random(seed)
-    width = rng.choice([128, 192, 256, 320, 384])
+    width = rng.choice([128, 192, 256, 352, 384])
     parts = rng.choice([g for g in (1, 2, 4, 8) if width % g == 0])
     layers = []
     for _ in range(rng.randint(2, 5)):
