@@ -5,7 +5,6 @@ long decoding; keys far away and at page borders made to stand out; the first
 tokens of a sequence; sizes that are 1 or equal; layers without a feed-forward;
 greedy generation through the engine."""
 import json
-import math
 import os
 import subprocess
 import sys
