@@ -713,11 +713,12 @@ IB_EXPORT int ib_attention_diff_mma(const void* q, const void* k_pool, const voi
         return IB_ERR_BAD_ARG;
     if (n_entries > 65535 || nkv > 65535) return IB_ERR_TOO_LARGE;
     const size_t smem = (size_t)(BM * QS + 2 * BN * KS + 2 * BN * VS) * sizeof(bf16);
+    const size_t smem1 = (size_t)(BM * QS + 2 * BN * KS) * sizeof(bf16);  // the first walk alone fetches no values: a CTA more an SM
     static bool configured = false;
     if (!configured) {
         cudaError_t ce = cudaFuncSetAttribute(attention_diff_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (ce == cudaSuccess)
-            ce = cudaFuncSetAttribute(attention_diff_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            ce = cudaFuncSetAttribute(attention_diff_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
         if (ce == cudaSuccess)
             ce = cudaFuncSetAttribute(attention_diff_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (ce != cudaSuccess) return (int)ce;
@@ -741,7 +742,7 @@ IB_EXPORT int ib_attention_diff_mma(const void* q, const void* k_pool, const voi
     float* stats = (float*)scratch;
     float* part = stats + (size_t)splits * n_rows * nh * 4;
     const dim3 grid((unsigned)tiles, n_entries, nkv * splits);
-    le = launch_kernel(attention_diff_mma_kernel<1>, grid, dim3(THREADS), smem, s, (const bf16*)q, (const bf16*)k_pool,
+    le = launch_kernel(attention_diff_mma_kernel<1>, grid, dim3(THREADS), smem1, s, (const bf16*)q, (const bf16*)k_pool,
                        (const bf16*)v_pool, (bf16*)out, cu_rows, positions, block_tables, max_blocks, nh, nkv, page_size,
                        num_pages, scale, cap, lambda, eps, out_scale, err, splits, slice_len, n_rows, stats, part);
     if (le != cudaSuccess) return (int)le;
